@@ -1,0 +1,380 @@
+#!/usr/bin/env python3
+"""Benchmark of the NVFP4 weight path on B200 (one JSON line on stdout, rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
+
+Headline (N = 1): the six fused sibling gemvs that share one input (K = 4096, outputs 4096, 4096,
+4096, 512, 64, 32; all NVFP4, M = 1) -- one launch of k_gemv_nvfp4 per step.  `value` is the
+achieved HBM rate in TB/s: algorithmic bytes of one step / device time of one step, inputs
+resident in HBM, the step rotating over weight copies whose total exceeds L2 several times.
+`e2e` is the same step through the C ABI with HOST buffers: the activation row is copied from
+pinned host memory and the six outputs are copied back inside the timed region (weights are
+model state and stay resident, as they do in the engine that calls this path).
+`sub` carries the other single-GPU configurations (single gemv [12288x4096]; siblings at
+M = 2, 4, 8; MoE decode layer at M = 1 and 4 with microseconds per layer; quantiser), each with
+its own byte count and fraction of the measured HBM peak.
+All data is synthetic: seeded N(0, 0.02) bf16 weights quantised by this library's bit-exact
+quantiser, N(0, 1) fp32 activations.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as G  # noqa: E402
+
+SIBLINGS = [4096, 4096, 4096, 512, 64, 32]
+K_HID = 4096
+L2_BYTES = 126e6
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = 'clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,' \
+        'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + self.Q,
+                                          '--format=csv,noheader,nounits', '-lms', '100'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True); self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(',')])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), r[2:6]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        if not sm:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        return {'sm_mhz': statistics.median(sm), 'sm_max_mhz': max(mx), 'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def nv_bytes(N, K):
+    return N * K // 2 + N * K // 16 + 4
+
+
+def time_graphs(graphs, steps, warmup, sampler=None):
+    """Replays one captured step per call, cycling over `graphs`; device time per step in ms."""
+    for i in range(warmup):
+        graphs[i % len(graphs)].replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        graphs[i % len(graphs)].replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def capture(fn):
+    g = torch.cuda.CUDAGraph()
+    fn(); torch.cuda.synchronize()                 # first call outside capture: attribute set-up
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def make_weight(P, N, K, seed):
+    gen = torch.Generator(device='cuda').manual_seed(seed)
+    w = (torch.randn((N, K), generator=gen, device='cuda') * 0.02).to(torch.bfloat16)
+    return P.quantize(w), w
+
+
+def clone_weight(P, W):
+    return P.Nvfp4Weight(W.packed.clone(), W.scale.clone(), W.gscale.clone())
+
+
+# ---- workloads --------------------------------------------------------------------------------
+
+def bench_siblings(P, M, steps, warmup, copies, sampler_index=None):
+    base = [make_weight(P, n, K_HID, 1000 + i)[0] for i, n in enumerate(SIBLINGS)]
+    sets = [base] + [[clone_weight(P, W) for W in base] for _ in range(copies - 1)]
+    x = torch.randn((M, K_HID), device='cuda', generator=torch.Generator(device='cuda').manual_seed(2))
+    ys = [torch.empty((M, n), device='cuda') for n in SIBLINGS]
+    jobs = [P.make_jobs(ws, [x] * 6, ys) for ws in sets]
+    graphs = [capture(lambda ws=ws, j=j: P.gemv_multi(ws, x, M, ys, jobs=j)) for ws, j in zip(sets, jobs)]
+    nbytes = sum(nv_bytes(n, K_HID) for n in SIBLINGS) + M * K_HID * 4 + M * sum(SIBLINGS) * 4
+    if sampler_index is None:
+        ms = time_graphs(graphs, steps, warmup)
+        return ms, nbytes, None, (sets, x, ys, jobs)
+    with ClockSampler(sampler_index) as cs:
+        ms = time_graphs(graphs, steps, warmup)
+        if steps * ms < 400:                        # keep the region long enough to be sampled
+            time_graphs(graphs, int(400 / max(ms, 1e-3)), 0)
+    return ms, nbytes, cs.summary(), (sets, x, ys, jobs)
+
+
+def bench_siblings_e2e(P, state, steps, warmup):
+    """Host buffers: x from pinned memory in, six outputs back to pinned memory, per step."""
+    sets, x, ys, jobs = state
+    M = x.shape[0]
+    xh = torch.randn((M, K_HID)).pin_memory()
+    yh = [torch.empty((M, n)).pin_memory() for n in SIBLINGS]
+    s = torch.cuda.current_stream()
+
+    def step(i):
+        x.copy_(xh, non_blocking=True)
+        P.gemv_multi(sets[i % len(sets)], x, M, ys, jobs=jobs[i % len(sets)])
+        for a, b in zip(yh, ys):
+            a.copy_(b, non_blocking=True)
+        s.synchronize()                            # the caller reads the result every step
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        step(i)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    return ms, M * K_HID * 4, M * sum(SIBLINGS) * 4
+
+
+def bench_gemv_single(P, steps, warmup, copies):
+    N = 12288
+    base, _ = make_weight(P, N, K_HID, 999)
+    ws = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
+    x = torch.randn((1, K_HID), device='cuda')
+    y = torch.empty((1, N), device='cuda')
+    graphs = [capture(lambda W=W: P.gemm(W, x, y)) for W in ws]
+    ms = time_graphs(graphs, steps, warmup)
+    return ms, nv_bytes(N, K_HID) + K_HID * 4 + N * 4
+
+
+def build_moe_layers(P, n_layers, H, I, E, topk, seed):
+    layers = []
+    for l in range(n_layers):
+        gen = torch.Generator(device='cuda').manual_seed(seed + l)
+        ex = []
+        for e in range(E + 1):
+            tr = []
+            for (o, i) in ((I, H), (I, H), (H, I)):
+                w = (torch.randn((o, i), generator=gen, device='cuda') * 0.02).to(torch.bfloat16)
+                tr.append(P.quantize(w))
+            ex.append(tuple(tr))
+        router = (torch.randn((E, H), generator=gen, device='cuda') * 0.02).to(torch.bfloat16)
+        bias = torch.randn(E, generator=gen, device='cuda') * 0.1
+        layers.append(P.MoeLayer(router, bias, ex[:E], ex[E], topk, H, I))
+    return layers
+
+
+def bench_moe(P, layers, M, steps, warmup):
+    H, I, E, topk = layers[0].hidden, layers[0].inter, layers[0].n_expert, layers[0].topk
+    gen = torch.Generator(device='cuda').manual_seed(77)
+    xs = [torch.randn((M, H), generator=gen, device='cuda') for _ in range(8)]
+    y = torch.empty((M, H), device='cuda'); sel = torch.empty((M, topk), dtype=torch.int32, device='cuda')
+    wts = torch.empty((M, topk), device='cuda')
+    combos = [(layers[i % len(layers)], xs[i % len(xs)]) for i in range(max(len(layers), len(xs)))]
+    graphs, distinct = [], []
+    for L, x in combos:
+        graphs.append(capture(lambda L=L, x=x: P.moe_forward(L, x, y, sel, wts)))
+        torch.cuda.synchronize()
+        distinct.append(len(set(sel.cpu().numpy().ravel().tolist())))
+    ms = time_graphs(graphs, steps, warmup)
+    per_expert = 3 * nv_bytes(I, H)
+    d = float(np.mean(distinct))
+    nbytes = (d + 1) * per_expert + E * H * 2 + E * 4 + 2 * M * H * 4 + M * topk * 8
+    return ms, nbytes, d
+
+
+def bench_quantize(P, steps, warmup):
+    N, K = 12288, K_HID
+    ws = [(torch.randn((N, K), device='cuda') * 0.02).to(torch.bfloat16) for _ in range(3)]
+    out = P.quantize(ws[0])
+    graphs = [capture(lambda w=w: P.quantize(w, out=out)) for w in ws]
+    ms = time_graphs(graphs, steps, warmup)
+    # two passes over the bf16 input (tensor amax, then codes) plus the NVFP4 output
+    return ms, 2 * N * K * 2 + nv_bytes(N, K)
+
+
+# ---- CPU baseline: the reference's CPU path restated (torch dequantise, then matmul) ------------
+
+def cpu_siblings_step(host_sets, x):
+    """reference ref/gen_moe.py:23-30 dequant + F.linear for the six sibling weights."""
+    import torch.nn.functional as F
+    KE2M1 = torch.tensor([0., .5, 1., 1.5, 2., 3., 4., 6.], dtype=torch.float32)
+    outs = []
+    for pk, sc, gs in host_sets:
+        out_f, in_f = pk.shape[0], pk.shape[1] * 2
+        flat = pk.reshape(-1)
+        low, high = flat & 0x0F, (flat >> 4) & 0x0F
+        comb = torch.stack((low, high), dim=1).reshape(out_f, in_f).long()
+        vals = KE2M1[comb & 7] * torch.where((comb & 8).bool(), -1.0, 1.0)
+        w = (vals.reshape(out_f, in_f // 16, 16) * (sc.float().reshape(out_f, in_f // 16, 1) / gs)).reshape(out_f, in_f)
+        outs.append(F.linear(x, w))
+    return outs
+
+
+def cpu_baseline(P, state, max_seconds=20.0):
+    sets, x, _, _ = state
+    host = [(W.packed.cpu(), W.scale.cpu().view(torch.float8_e4m3fn), W.gscale.cpu()) for W in sets[0]]
+    xh = x.cpu()
+    cpu_siblings_step(host, xh)                       # warm-up
+    n, t0 = 0, time.perf_counter()
+    while True:
+        cpu_siblings_step(host, xh); n += 1
+        el = time.perf_counter() - t0
+        if el > max_seconds or n >= 20:
+            break
+    return el / n, n
+
+
+# ---- main ---------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=2000)
+    ap.add_argument('--warmup', type=int, default=50)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--quick', action='store_true', help='headline only, no sub-workloads')
+    ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,siblings,moe,quant)')
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    peak, peak_kind = measured_peaks()
+    P = G.load_package()
+
+    if a.impl == 'reference':
+        return reference_arm(a, P, rank, peak)
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: there is no CPU fallback')
+    torch.cuda.set_device(local)
+    P.lib()                                            # fail now if the library is missing
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+        dist.barrier()
+        raise SystemExit('expert-parallel MoE bench is not wired yet')
+
+    copies = 10                                        # 10 x 29.7 MB = 297 MB per rotation, > 2x L2
+    ms, nbytes, clocks, state = bench_siblings(P, 1, a.steps, a.warmup, copies, sampler_index=local)
+    value = nbytes / (ms * 1e-3) / 1e12
+    e2e_ms, h2d, d2h = bench_siblings_e2e(P, state, min(a.steps, 2000), a.warmup)
+    sub = {}
+    only = set(filter(None, a.only.split(',')))
+    want = lambda k: not a.quick and (not only or k in only)
+    sub_steps = min(a.steps, 1000)
+    if want('gemv'):
+        m, b = bench_gemv_single(P, sub_steps, a.warmup, copies)
+        sub['gemv_12288x4096_M1'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
+                                      'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    if want('siblings'):
+        for M in (2, 4, 8):
+            m, b, _, _ = bench_siblings(P, M, sub_steps, a.warmup, copies)
+            sub['siblings_M%d' % M] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
+                                       'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    if want('moe'):
+        layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4000)
+        for M in (1, 4):
+            m, b, d = bench_moe(P, layers, M, sub_steps, a.warmup)
+            sub['moe_layer_I1536_M%d' % M] = {'us_per_layer': m * 1e3, 'bytes': b, 'distinct_routed': d,
+                                              'tbps': b / (m * 1e-3) / 1e12,
+                                              'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+        del layers
+    if want('quant'):
+        m, b = bench_quantize(P, min(sub_steps, 200), a.warmup)
+        sub['quantize_12288x4096'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
+                                      'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    cpu_s, cpu_n = cpu_baseline(P, state)
+    out = {
+        'metric': 'nvfp4_gemv_hbm_tbps', 'value': value, 'unit': 'TB/s', 'n_gpus': 1, 'steps': a.steps,
+        'warmup': a.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'nvfp4 weights (e2m1 + e4m3 scales), f16 products, f32 accumulate',
+        'data': 'synthetic',
+        'config': {'workload': 'six fused sibling NVFP4 gemvs sharing one input, K=4096, N=[4096,4096,4096,512,64,32], M=1 (configs[1])',
+                   'l2': 'inputs larger than L2: step i reads weight copy i mod %d (%.0f MB in rotation)' % (copies, copies * nbytes / 1e6),
+                   'math': 'fp32-mac' if P.lib() and os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'},
+        'roofline': {'bound': 'hbm', 'kernel': 'k_gemv_nvfp4<1,4>', 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
+                     'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': None,
+                     'algorithmic_bytes_per_launch': nbytes},
+        'e2e': {'value': nbytes / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
+                'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
+        'cpu_baseline': {'value': nbytes / cpu_s / 1e12, 'unit': 'TB/s', 'cores': torch.get_num_threads(),
+                         'kind': 'port', 'sample': '%d steps of the same six-sibling workload, torch dequantise + linear' % cpu_n,
+                         'ms_per_step': cpu_s * 1e3},
+        'gpu_launches': a.steps, 'clocks': clocks, 'sub': sub,
+    }
+    print(json.dumps(out))
+
+
+def reference_arm(a, P, rank, peak):
+    """The reference's CPU implementation of the path (its torch dequantise-then-matmul,
+    restated) on the host cores, on the headline workload."""
+    if rank != 0:
+        return
+    O = G.load_oracle()
+    rng = np.random.default_rng(1000)
+    host = []
+    for i, n in enumerate(SIBLINGS):
+        bits = O.f32_to_bf16_bits(np.random.default_rng(1000 + i).normal(0, 0.02, (n, K_HID)).astype(np.float32))
+        p, s, gs = O.quantize_tensor(O.bf16_bits_to_f32(bits))
+        host.append((torch.from_numpy(p), torch.from_numpy(s).view(torch.float8_e4m3fn), torch.from_numpy(gs)))
+    x = torch.from_numpy(rng.normal(0, 1, (1, K_HID)).astype(np.float32))
+    steps, warm = min(a.steps, 20), min(a.warmup, 3)
+    for _ in range(warm):
+        cpu_siblings_step(host, x)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_siblings_step(host, x)
+    sec = (time.perf_counter() - t0) / steps
+    nbytes = sum(nv_bytes(n, K_HID) for n in SIBLINGS) + K_HID * 4 + sum(SIBLINGS) * 4
+    v = nbytes / sec / 1e12
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'nvfp4_gemv_hbm_tbps', 'value': v, 'unit': 'TB/s', 'n_gpus': a.gpus,
+        'steps': steps, 'warmup': warm, 'ms_per_step': sec * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': 'six fused sibling NVFP4 gemvs sharing one input, K=4096, N=[4096,4096,4096,512,64,32], M=1 (configs[1])'},
+        'cpu_baseline': {'value': v, 'unit': 'TB/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': '%d full steps (bounded from --steps %d)' % (steps, a.steps)},
+        'e2e': {'value': v, 'unit': 'TB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }))
+
+
+if __name__ == '__main__':
+    main()

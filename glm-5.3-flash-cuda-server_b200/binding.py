@@ -1,0 +1,239 @@
+"""ctypes binding of libb200nvfp4.so for tests and benchmarks.
+
+The product is the shared library and its C ABI (include/b200_nvfp4.h); this file only moves
+pointers.  torch is used for device memory and streams.  There is no fallback of any kind: if
+the library has not been built, or a call returns a non-zero status, an exception is raised.
+"""
+import ctypes as C
+import os
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, 'libb200nvfp4.so')
+_lib = None
+
+F32, BF16 = 0, 1
+GEMV_MULTI_MAX, GEMV_M_MAX = 8, 8
+
+
+class WRef(C.Structure):
+    _fields_ = [('p', C.c_void_p), ('packed', C.c_void_p), ('scale', C.c_void_p), ('gscale', C.c_void_p)]
+
+
+class GemvJob(C.Structure):
+    _fields_ = [('y', C.c_void_p), ('W', WRef), ('x', C.c_void_p), ('N', C.c_int)]
+
+
+class Nvfp4Mat(C.Structure):
+    _fields_ = [('packed', C.c_void_p), ('scale', C.c_void_p), ('gscale', C.c_void_p)]
+
+
+class MoeLayerC(C.Structure):
+    _fields_ = [('router_w', WRef), ('router_bias', C.c_void_p), ('experts', C.c_void_p),
+                ('shared', C.c_void_p), ('n_expert', C.c_int), ('topk', C.c_int), ('hidden', C.c_int),
+                ('inter', C.c_int), ('routed_scale', C.c_float), ('swiglu_limit', C.c_float),
+                ('norm_topk', C.c_int)]
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded library; raises if it has not been built (python -c 'import __graft_entry__ as g; g.build()')."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error('libb200nvfp4.so is missing at %s: build it first; there is no CPU fallback' % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        vp, ci, st = C.c_void_p, C.c_int, C.c_size_t
+        L.b200_nvfp4_strerror.restype = C.c_char_p; L.b200_nvfp4_strerror.argtypes = [ci]
+        L.b200_nvfp4_version.restype = ci
+        L.b200_nvfp4_gemm.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp]
+        L.b200_nvfp4_gemv_multi.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp]
+        L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
+        L.b200_bf16_to_f32.argtypes = [vp, vp, st, vp]
+        L.b200_nvfp4_quantize.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
+        L.b200_nvfp4_dequantize.argtypes = [vp, C.POINTER(Nvfp4Mat), ci, ci, vp]
+        L.b200_moe_workspace_bytes.restype = st; L.b200_moe_workspace_bytes.argtypes = [C.POINTER(MoeLayerC), ci]
+        L.b200_moe_route.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, ci, vp]
+        L.b200_moe_forward.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
+        L.b200_moe_experts.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
+        _lib = L
+    return _lib
+
+
+EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
+           'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
+           'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts']
+
+
+def check(rc, what):
+    if rc != 0:
+        raise B200Error('%s failed: %s (%d)' % (what, lib().b200_nvfp4_strerror(rc).decode(), rc))
+
+
+def stream_ptr(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+class Nvfp4Weight:
+    """An NVFP4 triple resident on the device (packed u8 [N,K/2], scale u8 [N,K/16], gscale f32 [1])."""
+
+    def __init__(self, packed, scale, gscale, device='cuda'):
+        to = lambda a, dt: (torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a).to(device=device, dtype=dt).contiguous()
+        self.packed, self.scale, self.gscale = to(packed, torch.uint8), to(scale, torch.uint8), to(gscale, torch.float32)
+        self.N, self.K = self.packed.shape[0], self.packed.shape[1] * 2
+
+    def wref(self):
+        return WRef(None, self.packed.data_ptr(), self.scale.data_ptr(), self.gscale.data_ptr())
+
+    def mat(self):
+        return Nvfp4Mat(self.packed.data_ptr(), self.scale.data_ptr(), self.gscale.data_ptr())
+
+    def numpy(self):
+        return self.packed.cpu().numpy(), self.scale.cpu().numpy(), self.gscale.cpu().numpy()
+
+    @property
+    def nbytes(self):
+        return self.packed.numel() + self.scale.numel() + 4
+
+
+def gemm(W, x, y=None, dtype=BF16, stream=None):
+    """y[M,N] = x[M,K] . W^T.  W: Nvfp4Weight, or a bf16/f32 torch tensor [N,K]."""
+    x2 = x if x.dim() == 2 else x.unsqueeze(0)
+    M, K = x2.shape
+    if isinstance(W, Nvfp4Weight):
+        N, ref = W.N, W.wref()
+        assert W.K == K
+    else:
+        N, ref = W.shape[0], WRef(W.data_ptr(), None, None, None)
+        dtype = F32 if W.dtype == torch.float32 else BF16
+    if y is None:
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    check(lib().b200_nvfp4_gemm(_ptr(y), C.byref(ref), _ptr(x2), M, N, K, dtype, stream_ptr(stream)), 'b200_nvfp4_gemm')
+    return y if x.dim() == 2 else y[0]
+
+
+def gemv(W, x, y=None, stream=None):
+    return gemm(W, x, y, stream=stream)
+
+
+def make_jobs(weights, xs, ys):
+    arr = (GemvJob * len(weights))()
+    for i, (W, x, y) in enumerate(zip(weights, xs, ys)):
+        arr[i] = GemvJob(y.data_ptr(), W.wref(), x.data_ptr(), W.N)
+    return arr
+
+
+def gemv_multi(weights, xs, M=1, ys=None, stream=None, jobs=None):
+    """Fused group: weights share K; xs is one tensor [M,K] (shared) or a list (one per job)."""
+    if not isinstance(xs, (list, tuple)):
+        xs = [xs] * len(weights)
+    if ys is None:
+        ys = [torch.empty((M, W.N), dtype=torch.float32, device=xs[0].device) for W in weights]
+    if jobs is None:
+        jobs = make_jobs(weights, xs, ys)
+    check(lib().b200_nvfp4_gemv_multi(jobs, len(weights), M, weights[0].K, BF16, stream_ptr(stream)), 'b200_nvfp4_gemv_multi')
+    return ys
+
+
+def f32_to_bf16(src, stream=None):
+    dst = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    check(lib().b200_f32_to_bf16(_ptr(dst), _ptr(src), src.numel(), stream_ptr(stream)), 'b200_f32_to_bf16')
+    return dst
+
+
+def bf16_to_f32(src, stream=None):
+    dst = torch.empty(src.shape, dtype=torch.float32, device=src.device)
+    check(lib().b200_bf16_to_f32(_ptr(dst), _ptr(src), src.numel(), stream_ptr(stream)), 'b200_bf16_to_f32')
+    return dst
+
+
+def quantize(w_bf16, gscale_in=None, out=None, stream=None):
+    """bf16 [N,K] device tensor -> Nvfp4Weight, bit-exact with the reference quantiser."""
+    N, K = w_bf16.shape
+    dev = w_bf16.device
+    if out is None:
+        out = Nvfp4Weight(torch.empty((N, K // 2), dtype=torch.uint8, device=dev),
+                          torch.empty((N, K // 16), dtype=torch.uint8, device=dev),
+                          torch.empty(1, dtype=torch.float32, device=dev), device=dev)
+    check(lib().b200_nvfp4_quantize(_ptr(w_bf16), N, K, _ptr(out.packed), _ptr(out.scale), _ptr(out.gscale),
+                                    _ptr(gscale_in), stream_ptr(stream)), 'b200_nvfp4_quantize')
+    return out
+
+
+def dequantize(W, stream=None):
+    out = torch.empty((W.N, W.K), dtype=torch.float32, device=W.packed.device)
+    m = W.mat()
+    check(lib().b200_nvfp4_dequantize(_ptr(out), C.byref(m), W.N, W.K, stream_ptr(stream)), 'b200_nvfp4_dequantize')
+    return out
+
+
+class MoeLayer:
+    """Device-side description of one MoE layer: router, bias, expert pointer tables."""
+
+    def __init__(self, router_bf16, bias, experts, shared, topk, hidden, inter, routed_scale=2.5,
+                 swiglu_limit=10.0, norm_topk=True):
+        """experts: list of (gate, up, down) Nvfp4Weight; shared: one such triple or None."""
+        dev = router_bf16.device
+        self.router, self.bias, self.experts, self.shared = router_bf16, bias, experts, shared
+        flat = []
+        for g, u, d in experts:
+            for w in (g, u, d):
+                flat += [w.packed.data_ptr(), w.scale.data_ptr(), w.gscale.data_ptr()]
+        self.table = torch.tensor(flat, dtype=torch.int64).to(dev)
+        self.shared_table = None
+        if shared is not None:
+            fl = []
+            for w in shared:
+                fl += [w.packed.data_ptr(), w.scale.data_ptr(), w.gscale.data_ptr()]
+            self.shared_table = torch.tensor(fl, dtype=torch.int64).to(dev)
+        self.c = MoeLayerC(WRef(router_bf16.data_ptr(), None, None, None), bias.data_ptr(), self.table.data_ptr(),
+                           self.shared_table.data_ptr() if shared is not None else None,
+                           len(experts), topk, hidden, inter, routed_scale, swiglu_limit, 1 if norm_topk else 0)
+        self.topk, self.hidden, self.inter, self.n_expert = topk, hidden, inter, len(experts)
+        self._ws = {}
+
+    def workspace(self, M):
+        if M not in self._ws:
+            n = lib().b200_moe_workspace_bytes(C.byref(self.c), M)
+            self._ws[M] = torch.empty(n, dtype=torch.uint8, device=self.router.device)
+        return self._ws[M]
+
+
+def moe_route(layer, x, stream=None):
+    x2 = x if x.dim() == 2 else x.unsqueeze(0)
+    M = x2.shape[0]
+    sel = torch.empty((M, layer.topk), dtype=torch.int32, device=x.device)
+    wts = torch.empty((M, layer.topk), dtype=torch.float32, device=x.device)
+    logits = torch.empty((M, layer.n_expert), dtype=torch.float32, device=x.device)
+    check(lib().b200_moe_route(_ptr(x2), C.byref(layer.c), _ptr(sel), _ptr(wts), _ptr(logits), M, stream_ptr(stream)), 'b200_moe_route')
+    return sel, wts, logits
+
+
+def moe_forward(layer, x, y=None, sel=None, wts=None, stream=None):
+    x2 = x if x.dim() == 2 else x.unsqueeze(0)
+    M = x2.shape[0]
+    dev = x.device
+    y = torch.empty((M, layer.hidden), dtype=torch.float32, device=dev) if y is None else y
+    sel = torch.empty((M, layer.topk), dtype=torch.int32, device=dev) if sel is None else sel
+    wts = torch.empty((M, layer.topk), dtype=torch.float32, device=dev) if wts is None else wts
+    ws = layer.workspace(M)
+    check(lib().b200_moe_forward(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), _ptr(ws), M, stream_ptr(stream)), 'b200_moe_forward')
+    return y, sel, wts
+
+
+def moe_experts(layer, x, sel, wts, y=None, stream=None):
+    x2 = x if x.dim() == 2 else x.unsqueeze(0)
+    M = x2.shape[0]
+    y = torch.empty((M, layer.hidden), dtype=torch.float32, device=x.device) if y is None else y
+    ws = layer.workspace(M)
+    check(lib().b200_moe_experts(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), _ptr(ws), M, stream_ptr(stream)), 'b200_moe_experts')
+    return y

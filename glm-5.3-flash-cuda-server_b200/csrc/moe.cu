@@ -1,0 +1,268 @@
+// moe.cu -- MoE block for sm_100a: sigmoid router with bias-ranked top-k, routed + shared NVFP4
+// SwiGLU experts, gate-weighted sum.  Replaces the reference's kernels/moe.cu (k_route :126-156,
+// k_expert_act :175-259, k_expert_down :270-327, k_down_combine :584-597, entry points :602-740).
+//
+// Launches per layer: router logits (bf16 gemm), k_route, k_expert_act, k_expert_down.
+//   k_expert_act   one warp owns two intermediate indices o, o+1 of one (token, slot): the gate
+//                  and up rows of both stream together (4 rows x 2 steps in flight per lane),
+//                  and the clamped SwiGLU is applied before anything is written.
+//   k_expert_down  one warp owns one hidden row of one token and walks the slots three at a
+//                  time, each slot against its own staged intermediate vector; the gate
+//                  weight, 1/gscale and the staging scale are folded per slot at lane level and
+//                  the warp is reduced once, in a fixed order -- so the per-slot partial buffer
+//                  and the separate combine launch of the reference are gone, and results are
+//                  identical from run to run (no atomics).
+// Geometry (hidden, inter, top-k, scale, clamp) is per layer at run time.
+#include "b200_internal.h"
+#include "gemv_core.cuh"
+#include <cstdio>
+
+namespace b200 {
+
+constexpr int ROUTE_MAXC = 16;        // candidates per lane -> n_expert <= 512
+constexpr int MOE_MAX_SLOTS = 17;     // topk <= 16, plus the shared expert
+
+struct MoeArgs {
+    const float* x; float* y; const int32_t* sel; const float* wts; float* act;
+    const b200_nvfp4_mat* experts; const b200_nvfp4_mat* shared;
+    int M, H, I, E, topk, ns;
+    float limit;
+};
+
+// One warp per token.  Ranking value = sigmoid(logit) + bias, gate value = sigmoid(logit);
+// among equal ranking values the lowest expert index wins, as in the reference's serial scan
+// with a strict '>' (kernels/moe.cu:146-152).
+__global__ void __launch_bounds__(32)
+k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restrict__ logits,
+        const float* __restrict__ bias, int E, int K, float scaling, int norm_prob) {
+    const int tok = blockIdx.x, lane = threadIdx.x;
+    logits += (size_t)tok * E; sel += (size_t)tok * K; wts += (size_t)tok * K;
+    float score[ROUTE_MAXC], choice[ROUTE_MAXC];
+    #pragma unroll
+    for (int j = 0; j < ROUTE_MAXC; ++j) {
+        const int i = lane + 32 * j;
+        if (i < E) {
+            score[j] = 1.f / (1.f + __expf(-logits[i]));
+            choice[j] = score[j] + bias[i];
+        } else { score[j] = 0.f; choice[j] = -3.0e38f; }
+    }
+    float my_w = 0.f;                              // lane k keeps the k-th gate
+    for (int k = 0; k < K; ++k) {
+        float bv = -1e30f, bs = 0.f; int bi = 0x7fffffff;
+        #pragma unroll
+        for (int j = 0; j < ROUTE_MAXC; ++j)
+            if (choice[j] > bv) { bv = choice[j]; bs = score[j]; bi = lane + 32 * j; }
+        #pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bs = os; bi = oi; }
+        }
+        if (bi >= E) bi = 0;                       // only if fewer than K finite candidates
+        #pragma unroll
+        for (int j = 0; j < ROUTE_MAXC; ++j) if (lane + 32 * j == bi) choice[j] = -1e30f;
+        if (lane == k) my_w = bs;
+        if (lane == 0) sel[k] = bi;
+    }
+    float d = 1.f;
+    if (norm_prob) {
+        d = 1e-20f;
+        for (int k = 0; k < K; ++k) d += __shfl_sync(0xffffffffu, my_w, k);
+    }
+    if (lane < K) wts[lane] = my_w / d * scaling;
+}
+
+template <int MATH>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_expert_act(const __grid_constant__ MoeArgs a, int tiles, int total_tasks) {
+    extern __shared__ uint4 xs[];
+    __shared__ float inv_s[1];
+    __shared__ float red[GEMV_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int staged = -1;
+    for (int task = blockIdx.x; task < total_tasks; task += gridDim.x) {
+        const int m = task / (a.ns * tiles), rem = task - m * (a.ns * tiles);
+        const int slot = rem / tiles, tile = rem - slot * tiles;
+        if (m != staged) {
+            if (staged >= 0) __syncthreads();
+            stage_x(a.x + (size_t)m * a.H, 1, a.H, xs, inv_s, red);
+            staged = m;
+        }
+        const int o0 = tile * (GEMV_WARPS * 2) + warp * 2;
+        if (o0 >= a.I) continue;
+        const b200_nvfp4_mat* mats;
+        if (slot < a.topk) {
+            int e = a.sel[(size_t)m * a.topk + slot];
+            e = e < 0 ? 0 : (e >= a.E ? a.E - 1 : e);
+            mats = a.experts + (size_t)e * 3;
+        } else mats = a.shared;
+        const b200_nvfp4_mat G = mats[0], U = mats[1];
+        const int o1 = min(o0 + 1, a.I - 1);
+        const size_t pr = (size_t)a.H >> 1, sr = (size_t)a.H >> 4;
+        RowPtr rows[4] = {{G.packed + o0 * pr, G.scale + o0 * sr}, {U.packed + o0 * pr, U.scale + o0 * sr},
+                          {G.packed + o1 * pr, G.scale + o1 * sr}, {U.packed + o1 * pr, U.scale + o1 * sr}};
+        float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
+        warp_rows<1, 4, MATH>(rows, a.H, xs, acc, lane);
+        const float kg = inv_s[0] / G.gscale[0], ku = inv_s[0] / U.gscale[0];
+        #pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            float g = warp_sum(acc[2 * q][0]) * kg, u = warp_sum(acc[2 * q + 1][0]) * ku;
+            if (lane == 0 && o0 + q < a.I) {
+                g = fminf(g, a.limit);
+                u = fminf(fmaxf(u, -a.limit), a.limit);
+                a.act[((size_t)m * a.ns + slot) * a.I + o0 + q] = (g / (1.f + __expf(-g))) * u;
+            }
+        }
+    }
+}
+
+template <int MATH>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_expert_down(const __grid_constant__ MoeArgs a, int tiles, int total_tasks) {
+    extern __shared__ uint4 xs[];
+    __shared__ float inv_s[MOE_MAX_SLOTS];
+    __shared__ float red[MOE_MAX_SLOTS * GEMV_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int stride = xs_chunks(a.I);
+    int staged = -1;
+    for (int task = blockIdx.x; task < total_tasks; task += gridDim.x) {
+        const int m = task / tiles, tile = task - m * tiles;
+        if (m != staged) {
+            if (staged >= 0) __syncthreads();
+            stage_x(a.act + (size_t)m * a.ns * a.I, a.ns, a.I, xs, inv_s, red);
+            staged = m;
+        }
+        const int h = tile * GEMV_WARPS + warp;
+        if (h >= a.H) continue;
+        const size_t pr = (size_t)a.I >> 1, sr = (size_t)a.I >> 4;
+        float tot = 0.f;
+        for (int s0 = 0; s0 < a.ns; s0 += 3) {
+            RowPtr rows[3]; const uint4* xb[3]; float coef[3];
+            #pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const int slot = min(s0 + q, a.ns - 1);
+                const b200_nvfp4_mat* mats;
+                float w = 1.f;
+                if (slot < a.topk) {
+                    int e = a.sel[(size_t)m * a.topk + slot];
+                    e = e < 0 ? 0 : (e >= a.E ? a.E - 1 : e);
+                    mats = a.experts + (size_t)e * 3;
+                    w = a.wts[(size_t)m * a.topk + slot];
+                } else mats = a.shared;
+                const b200_nvfp4_mat D = mats[2];
+                rows[q].p = D.packed + h * pr; rows[q].s = D.scale + h * sr;
+                xb[q] = xs + (size_t)slot * stride;
+                coef[q] = (s0 + q < a.ns) ? w * inv_s[slot] / D.gscale[0] : 0.f;
+            }
+            float acc[3] = {0.f, 0.f, 0.f};
+            warp_rows_own_x<3, MATH>(rows, a.I, xb, acc, lane);
+            tot = fmaf(acc[0], coef[0], tot);
+            tot = fmaf(acc[1], coef[1], tot);
+            tot = fmaf(acc[2], coef[2], tot);
+        }
+        tot = warp_sum(tot);
+        if (lane == 0) a.y[(size_t)m * a.H + h] = tot;
+    }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int check_layer(const b200_moe_layer* L, int M) {
+    if (!L || M < 1) return B200_EINVAL;
+    if (!L->experts || L->n_expert < 1 || L->topk < 1 || L->topk > 16 || L->topk > L->n_expert) return B200_EINVAL;
+    if (L->n_expert > 32 * ROUTE_MAXC) return B200_ELIMIT;
+    if (L->hidden <= 0 || L->inter <= 0 || (L->hidden & 31) || (L->inter & 31)) return B200_ESHAPE;
+    if ((size_t)xs_chunks(L->hidden) * 16 > 200 * 1024 ||
+        (size_t)(L->topk + 1) * xs_chunks(L->inter) * 16 > 200 * 1024) return B200_ELIMIT;
+    return B200_OK;
+}
+
+template <typename Kern>
+static int grid_for(Kern kern, size_t smem, int tasks, int* grid) {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return launch_failed("moe: cudaFuncSetAttribute");
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem) != cudaSuccess || occ < 1)
+        return launch_failed("moe: occupancy query");
+    *grid = std::min(tasks, sm_count() * occ);
+    return B200_OK;
+}
+
+static int experts_forward(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
+                           const float* wts, float* act, int M, cudaStream_t s) {
+    MoeArgs a{};
+    a.x = x; a.y = y; a.sel = sel; a.wts = wts; a.act = act;
+    a.experts = L->experts; a.shared = L->shared;
+    a.M = M; a.H = L->hidden; a.I = L->inter; a.E = L->n_expert; a.topk = L->topk;
+    a.ns = L->topk + (L->shared ? 1 : 0);
+    a.limit = L->swiglu_limit;
+    const int math = nvfp4_math_mode();
+    {
+        const int tiles = (a.I + GEMV_WARPS * 2 - 1) / (GEMV_WARPS * 2), tasks = M * a.ns * tiles;
+        const size_t smem = (size_t)xs_chunks(a.H) * 16;
+        int grid = 0;
+        if (math) {
+            if (int rc = grid_for(k_expert_act<1>, smem, tasks, &grid)) return rc;
+            k_expert_act<1><<<grid, GEMV_THREADS, smem, s>>>(a, tiles, tasks);
+        } else {
+            if (int rc = grid_for(k_expert_act<0>, smem, tasks, &grid)) return rc;
+            k_expert_act<0><<<grid, GEMV_THREADS, smem, s>>>(a, tiles, tasks);
+        }
+        if (int rc = check_launch("k_expert_act")) return rc;
+    }
+    {
+        const int tiles = (a.H + GEMV_WARPS - 1) / GEMV_WARPS, tasks = M * tiles;
+        const size_t smem = (size_t)a.ns * xs_chunks(a.I) * 16;
+        int grid = 0;
+        if (math) {
+            if (int rc = grid_for(k_expert_down<1>, smem, tasks, &grid)) return rc;
+            k_expert_down<1><<<grid, GEMV_THREADS, smem, s>>>(a, tiles, tasks);
+        } else {
+            if (int rc = grid_for(k_expert_down<0>, smem, tasks, &grid)) return rc;
+            k_expert_down<0><<<grid, GEMV_THREADS, smem, s>>>(a, tiles, tasks);
+        }
+        if (int rc = check_launch("k_expert_down")) return rc;
+    }
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Workspace: logits f32 [M, E] | act f32 [M, topk+1, inter], each part 256-byte aligned.
+extern "C" size_t b200_moe_workspace_bytes(const b200_moe_layer* L, int M) {
+    if (!L || M < 1) return 0;
+    return align_up((size_t)M * L->n_expert * 4, 256) + align_up((size_t)M * (L->topk + 1) * L->inter * 4, 256);
+}
+
+extern "C" int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts,
+                              float* logits, int M, b200_stream stream) {
+    if (int rc = check_layer(L, M)) return rc;
+    if (!x || !sel || !wts || !logits || !L->router_bias) return B200_EINVAL;
+    if (int rc = b200_nvfp4_gemm(logits, &L->router_w, x, M, L->n_expert, L->hidden, B200_BF16, stream)) return rc;
+    k_route<<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk,
+                                  L->routed_scale, L->norm_topk);
+    return check_launch("k_route");
+}
+
+extern "C" int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
+                                const float* wts, void* ws, int M, b200_stream stream) {
+    if (int rc = check_layer(L, M)) return rc;
+    if (!x || !y || !sel || !wts || !ws) return B200_EINVAL;
+    if ((uintptr_t)ws & 15) return B200_EALIGN;
+    float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));
+    return experts_forward(x, L, y, sel, wts, act, M, stream);
+}
+
+extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
+                                float* wts, void* ws, int M, b200_stream stream) {
+    if (int rc = check_layer(L, M)) return rc;
+    if (!x || !y || !sel || !wts || !ws) return B200_EINVAL;
+    if ((uintptr_t)ws & 15) return B200_EALIGN;
+    float* logits = static_cast<float*>(ws);
+    if (int rc = b200_moe_route(x, L, sel, wts, logits, M, stream)) return rc;
+    return b200_moe_experts(x, L, y, sel, wts, ws, M, stream);
+}

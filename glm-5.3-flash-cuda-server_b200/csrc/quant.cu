@@ -1,0 +1,170 @@
+// quant.cu -- bf16 -> NVFP4 quantiser and NVFP4 -> fp32 dequantiser for sm_100a.
+//
+// Bit-exact with the reference's numpy quantiser (tools/requant_dense_nvfp4.py:53-68 quant_block,
+// :209-215 global scale).  What "bit-exact" forces here:
+//   * every step is one IEEE fp32 operation in the reference's order (amax/6, *gs, clip,
+//     e4m3(code)/gs, w/eff): no FMA contraction, no approximate division -- the expressions use
+//     __fdiv_rn / __fmul_rn so the compiler cannot fuse or reorder them;
+//   * code selection is numpy's searchsorted(mid, v) = "number of mid-points strictly below v",
+//     so a value exactly on a mid-point takes the LOWER code; the hardware converters round such
+//     ties to even, which is why cvt.rn.satfinite.e2m1x2 / e4m3x2 are not used here;
+//   * the global scale is a double-precision quotient rounded once to fp32.
+// HBM-bound: 2 B read and 0.5625 B written per weight; one thread owns one 16-group (32 B in,
+// 8 B + 1 B out), consecutive threads own consecutive groups, so every access is coalesced.
+#include "b200_internal.h"
+#include "nvfp4_decode.cuh"
+
+namespace b200 {
+
+// amax over the tensor.  Non-negative floats order like their bit patterns, so an unsigned
+// atomicMax on the bits is an exact, order-independent float max.
+__global__ void __launch_bounds__(256)
+k_amax_bf16(const uint4* __restrict__ w, size_t n_vec, const __nv_bfloat16* __restrict__ tail,
+            size_t n_tail, uint32_t* __restrict__ out_bits) {
+    float a = 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = w[i];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            a = fmaxf(a, fabsf(__uint_as_float(u[j] << 16)));
+            a = fmaxf(a, fabsf(__uint_as_float(u[j] & 0xffff0000u)));
+        }
+    }
+    if (blockIdx.x == 0)
+        for (size_t i = threadIdx.x; i < n_tail; i += blockDim.x) a = fmaxf(a, fabsf(__bfloat162float(tail[i])));
+    a = warp_max(a);
+    if ((threadIdx.x & 31) == 0 && a > 0.f) atomicMax(out_bits, __float_as_uint(a));
+}
+
+// In place: amax bits -> gs = fp32(2688 / max(amax, 1e-12)), quotient in double.
+__global__ void k_finish_gs(float* gs) {
+    double d = (double)gs[0];
+    if (!(d >= 1e-12)) d = 1e-12;
+    gs[0] = (float)((448.0 * 6.0) / d);
+}
+
+// Largest e4m3 code (0..126) whose value is <= s, for 0 <= s <= 448, from the float's fields.
+__device__ __forceinline__ int e4m3_floor_code(float s) {
+    if (s < 0.015625f) return (int)(s * 512.f);              // subnormal codes: value = m / 512
+    const uint32_t b = __float_as_uint(s);
+    return (int)((((b >> 23) - 120u) << 3) | ((b >> 20) & 7u));
+}
+
+__device__ __forceinline__ int e2m1_index(float a) {          // #{mid < a}, mids of the e2m1 grid
+    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+}
+
+__global__ void __launch_bounds__(256)
+k_quantize(const __nv_bfloat16* __restrict__ w, size_t n_groups, const float* __restrict__ gsp,
+           uint8_t* __restrict__ packed, uint8_t* __restrict__ scale, bool vec_in, bool vec_out) {
+    const float gs = gsp[0];
+    for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups;
+         g += (size_t)gridDim.x * blockDim.x) {
+        float v[16];
+        if (vec_in) {
+            const uint4 a = reinterpret_cast<const uint4*>(w)[2 * g], b = reinterpret_cast<const uint4*>(w)[2 * g + 1];
+            const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[2 * j] = __uint_as_float(u[j] << 16);
+                v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+            }
+        } else {
+            #pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(w[16 * g + j]);
+        }
+        float amax = 0.f;
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
+        s = fminf(fmaxf(s, 0.f), 448.f);
+        int code = e4m3_floor_code(s);
+        if (code < 126) {
+            const float mid = __fmul_rn(__fadd_rn(e4m3_to_f32(code + 1), e4m3_to_f32(code)), 0.5f);
+            code += (mid < s) ? 1 : 0;
+        }
+        const float eff = fmaxf(__fdiv_rn(e4m3_to_f32(code), gs), 1e-30f);
+        uint32_t lo = 0, hi = 0;
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float q = __fdiv_rn(v[j], eff);
+            uint32_t c = (uint32_t)e2m1_index(fabsf(q));
+            if (c != 0 && (__float_as_uint(q) >> 31)) c |= 8u;
+            if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
+        }
+        if (vec_out) {
+            reinterpret_cast<uint2*>(packed)[g] = make_uint2(lo, hi);
+        } else {
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) { packed[8 * g + j] = (uint8_t)(lo >> (8 * j)); packed[8 * g + 4 + j] = (uint8_t)(hi >> (8 * j)); }
+        }
+        scale[g] = (uint8_t)code;
+    }
+}
+
+// out[n,k] = e2m1(nib) * (e4m3(scale) / gs): the operation order of reference
+// ref/gen_moe.py:29, so results compare bit for bit.
+__global__ void __launch_bounds__(256)
+k_dequantize(float* __restrict__ out, const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scale,
+             const float* __restrict__ gsp, size_t n_groups) {
+    const float gs = gsp[0];
+    for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups;
+         g += (size_t)gridDim.x * blockDim.x) {
+        const float sc = __fdiv_rn(e4m3_to_f32(scale[g]), gs);
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t b = packed[8 * g + j];
+            const float mag[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+            const float l = mag[b & 7], h = mag[(b >> 4) & 7];
+            out[16 * g + 2 * j] = __fmul_rn((b & 8) ? -l : l, sc);
+            out[16 * g + 2 * j + 1] = __fmul_rn((b & 0x80) ? -h : h, sc);
+        }
+    }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_nvfp4_quantize(const void* w_bf16, int N, int K, uint8_t* packed, uint8_t* scale,
+                                   float* gscale, const float* gscale_in, b200_stream stream) {
+    if (N < 0 || K <= 0 || (!gscale && !gscale_in)) return B200_EINVAL;
+    if (N > 0 && (!w_bf16 || !packed || !scale)) return B200_EINVAL;      // N == 0: only gscale is written
+    if (K & 15) return B200_ESHAPE;
+    if (((uintptr_t)w_bf16 & 1) || (gscale && ((uintptr_t)gscale & 3))) return B200_EALIGN;
+    const size_t n = (size_t)N * K;
+    const int grid_cap = sm_count() * 8;
+    const float* gs = gscale_in;
+    if (!gscale_in) {
+        if (cudaMemsetAsync(gscale, 0, 4, stream) != cudaSuccess) return launch_failed("quantize: memset");
+        if (n) {
+            const bool al = ((uintptr_t)w_bf16 & 15) == 0;
+            const size_t n_vec = al ? n / 8 : 0, n_tail = n - n_vec * 8;
+            const int grid = (int)std::min<size_t>((n_vec + 255) / 256 + 1, grid_cap);
+            k_amax_bf16<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(w_bf16), n_vec,
+                static_cast<const __nv_bfloat16*>(w_bf16) + n_vec * 8, n_tail, reinterpret_cast<uint32_t*>(gscale));
+            if (int rc = check_launch("k_amax_bf16")) return rc;
+        }
+        k_finish_gs<<<1, 1, 0, stream>>>(gscale);
+        if (int rc = check_launch("k_finish_gs")) return rc;
+        gs = gscale;
+    }
+    if (n == 0) return B200_OK;
+    const size_t groups = n / 16;
+    const int grid = (int)std::min<size_t>((groups + 255) / 256, grid_cap);
+    k_quantize<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w_bf16), groups, gs, packed, scale,
+                                         ((uintptr_t)w_bf16 & 15) == 0, ((uintptr_t)packed & 7) == 0);
+    return check_launch("k_quantize");
+}
+
+extern "C" int b200_nvfp4_dequantize(float* out, const b200_nvfp4_mat* W, int N, int K, b200_stream stream) {
+    if (!out || !W || !W->packed || !W->scale || !W->gscale || N < 0 || K <= 0) return B200_EINVAL;
+    if (K & 15) return B200_ESHAPE;
+    const size_t groups = (size_t)N * K / 16;
+    if (groups == 0) return B200_OK;
+    const int grid = (int)std::min<size_t>((groups + 255) / 256, sm_count() * 8);
+    k_dequantize<<<grid, 256, 0, stream>>>(out, W->packed, W->scale, W->gscale, groups);
+    return check_launch("k_dequantize");
+}

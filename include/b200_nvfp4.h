@@ -1,0 +1,131 @@
+/* b200_nvfp4.h -- C ABI of the B200 (sm_100a) NVFP4 weight-path library, libb200nvfp4.so.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its comment says
+ * host; every call enqueues on `stream` and returns without synchronising.  Return value:
+ * 0 on success, a B200_E* code otherwise (b200_nvfp4_strerror names it).  The library owns
+ * no device memory, has no CPU fallback, and keeps no state between calls besides cached
+ * device attributes.
+ *
+ * NVFP4 tensor = three buffers (reference include/nvfp4.cuh:3-7):
+ *   packed [N, K/2] u8, low nibble = even k;  scale [N, K/16] u8 fp8-e4m3;  gscale [1] f32
+ *   w[n,k] = e2m1(nibble) * e4m3(scale[n,k/16]) / gscale[0]
+ * Activations and outputs are fp32 row-major: x[M,K], y[M,N].
+ */
+#ifndef B200_NVFP4_H
+#define B200_NVFP4_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b200_stream;      /* same type as cudaStream_t */
+
+enum {
+    B200_OK = 0,
+    B200_EINVAL = 1,      /* null pointer, non-positive size, M out of range */
+    B200_ESHAPE = 2,      /* K not a multiple of 16, or a shape the kernel cannot tile */
+    B200_EALIGN = 3,      /* pointer below the 4-byte floor the format guarantees */
+    B200_ELAUNCH = 4,     /* the CUDA runtime refused the launch (cudaGetLastError text logged) */
+    B200_ELIMIT = 5,      /* size beyond a documented maximum */
+    B200_ENOTIMPL = 6
+};
+enum { B200_F32 = 0, B200_BF16 = 1 };          /* dtype of a non-quantised weight (gemv.h:13) */
+enum { B200_GEMV_MULTI_MAX = 8, B200_GEMV_M_MAX = 8 };
+
+/* Weight handle.  Mirrors glm5::WRef (reference include/gemv.h:16-26): a plain row-major
+ * [N,K] buffer of `dtype`, or an NVFP4 triple, which wins whenever `packed` is non-null. */
+typedef struct {
+    const void*    p;
+    const uint8_t* packed;
+    const uint8_t* scale;
+    const float*   gscale;
+} b200_wref;
+
+/* One gemv of a fused group.  Mirrors glm5::GemvJob (reference include/gemv.h:50-55);
+ * x is [M,K], y is [M,N] for the M given to the call. */
+typedef struct {
+    float*       y;
+    b200_wref    W;
+    const float* x;
+    int          N;
+} b200_gemv_job;
+
+/* Mirrors glm5::Nvfp4Mat (reference include/moe.h:13-17). */
+typedef struct {
+    const uint8_t* packed;
+    const uint8_t* scale;
+    const float*   gscale;
+} b200_nvfp4_mat;
+
+/* Mirrors glm5::MoeLayer (reference include/moe.h:19-26) plus the geometry the reference
+ * bakes in at compile time (include/glm5_config.h:20, 84-91), here per layer at run time. */
+typedef struct {
+    b200_wref             router_w;      /* bf16 [n_expert, hidden] */
+    const float*          router_bias;   /* f32 [n_expert] */
+    const b200_nvfp4_mat* experts;       /* DEVICE array, 3*n_expert: [3e]=gate [3e+1]=up [3e+2]=down */
+    const b200_nvfp4_mat* shared;        /* DEVICE array of 3, or null for no shared expert */
+    int   n_expert;
+    int   topk;                          /* <= 16 */
+    int   hidden;                        /* multiple of 32 */
+    int   inter;                         /* multiple of 32 */
+    float routed_scale;                  /* 2.5 in the reference */
+    float swiglu_limit;                  /* 10 in the reference */
+    int   norm_topk;                     /* 1: renormalise the selected gates */
+} b200_moe_layer;
+
+const char* b200_nvfp4_strerror(int code);
+int         b200_nvfp4_version(void);
+
+/* y[M,N] = x[M,K] . W[N,K]^T.  Replaces glm5::gemm / glm5::gemv (reference include/gemv.h:29,
+ * 75; kernels/gemv.cu:369-396, 456-465, 649-701).  Any M >= 1: rows are processed in chunks of
+ * up to 8 and W is re-read once per chunk.  Each output row of y depends only on its own row
+ * of x, and the result is bit-identical from run to run. */
+int b200_nvfp4_gemm(float* y, const b200_wref* W, const float* x, int M, int N, int K,
+                    int dtype, b200_stream stream);
+
+/* n (1..8) gemvs that share K, M (1..8) and dtype, in ONE launch; jobs is a HOST array.
+ * Replaces glm5::gemv_multi (reference include/gemv.h:56, kernels/gemv.cu:404-435), widened
+ * from 4 jobs at M=1 to 8 jobs at M<=8.  Bit-identical to n separate b200_nvfp4_gemm calls. */
+int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
+                          b200_stream stream);
+
+/* Element-wise converters (reference include/gemv.h:61-62, kernels/gemv.cu:470-488). */
+int b200_f32_to_bf16(void* dst_bf16, const float* src, size_t n, b200_stream stream);
+int b200_bf16_to_f32(float* dst, const void* src_bf16, size_t n, b200_stream stream);
+
+/* bf16 [N,K] -> NVFP4 triple, bit-exact with the reference quantiser (tools/
+ * requant_dense_nvfp4.py:53-68 quant_block and :209-215 global scale).  Outputs are caller
+ * allocated: packed N*K/2 bytes, scale N*K/16 bytes, gscale 4 bytes.  If `gscale_in` is
+ * non-null the tensor pass is skipped and that scale is used (activation re-quantisation). */
+int b200_nvfp4_quantize(const void* w_bf16, int N, int K, uint8_t* packed, uint8_t* scale,
+                        float* gscale, const float* gscale_in, b200_stream stream);
+
+/* NVFP4 triple -> fp32 [N,K] (reference ref/gen_moe.py:23-30); a test and tooling helper. */
+int b200_nvfp4_dequantize(float* out, const b200_nvfp4_mat* W, int N, int K, b200_stream stream);
+
+/* Workspace for M tokens of one MoE layer, in bytes (reference include/moe.h:28-29,
+ * kernels/moe.cu:602, 621-625 count floats; the drop-in header converts). */
+size_t b200_moe_workspace_bytes(const b200_moe_layer* L, int M);
+
+/* Router only: logits[M,E] = x.Wr^T, sel int32 [M,topk] in descending (score+bias) order,
+ * wts f32 [M,topk] (reference include/moe.h:34-35, 44-45; kernels/moe.cu:126-156, 638-650). */
+int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts,
+                   float* logits, int M, b200_stream stream);
+
+/* Whole block, M tokens: route, top-k SwiGLU experts, shared expert, gate-weighted sum in a
+ * fixed order (reference include/moe.h:32-33, 41-43; kernels/moe.cu:669-740).  x,y [M,hidden];
+ * sel/wts [M,topk] are outputs; ws holds b200_moe_workspace_bytes(L, M) bytes. */
+int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
+                     float* wts, void* ws, int M, b200_stream stream);
+
+/* Expert half only, routing supplied by the caller (sel/wts are inputs).  No counterpart in
+ * the reference, which always routes itself; used where routing is decided elsewhere. */
+int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
+                     const float* wts, void* ws, int M, b200_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_NVFP4_H */

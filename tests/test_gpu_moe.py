@@ -1,0 +1,158 @@
+"""GPU parity for the MoE block through the C ABI: routing identical to the oracle as a set,
+gate weights within 1e-5, layer output within rel-L2 1e-3 / max-abs 2e-2 (reference gate:
+tests/gate_moe.cu:133-162 compares routing as a set and y by cosine / max_rel)."""
+import ctypes as C
+import numpy as np
+import pytest
+import torch
+
+from util import pkg, oracle, host_triple, seeded_bf16, to_dev_bf16, ref_kernels, REL_TOL, ABS_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def build_layer(H, I, E, topk, seed, shared=True, on_gpu=False, router_std=0.02, bias_std=0.1):
+    """Returns (device layer, host description for the oracle).  on_gpu: weights are drawn and
+    quantised on the device (the quantiser is proven bit-exact separately) and only the experts
+    a test needs are copied back."""
+    P, O = pkg(), oracle()
+    rng = np.random.default_rng(seed)
+    rb = O.f32_to_bf16_bits(rng.normal(0, router_std, (E, H)).astype(np.float32))
+    bias = rng.normal(0, bias_std, E).astype(np.float32)
+    n = E + (1 if shared else 0)
+    dev = []
+    if on_gpu:
+        g = torch.Generator(device='cuda').manual_seed(seed)
+        for e in range(n):
+            tr = []
+            for (o, i) in ((I, H), (I, H), (H, I)):
+                w = (torch.randn((o, i), generator=g, device='cuda') * 0.02).to(torch.bfloat16)
+                tr.append(P.quantize(w))
+            dev.append(tuple(tr))
+        host = None
+    else:
+        host = [(host_triple((I, H), seed * 1000 + 3 * e), host_triple((I, H), seed * 1000 + 3 * e + 1),
+                 host_triple((H, I), seed * 1000 + 3 * e + 2)) for e in range(n)]
+        dev = [tuple(P.Nvfp4Weight(*w) for w in t) for t in host]
+    layer = P.MoeLayer(to_dev_bf16(rb), torch.from_numpy(bias).cuda(), dev[:E], dev[E] if shared else None,
+                       topk, H, I)
+    return layer, dict(rb=rb, bias=bias, host=host, dev=dev, E=E, topk=topk, shared=shared)
+
+
+def host_experts(d, needed):
+    """Oracle-side (gate, up, down) triples; experts not in `needed` are left as None."""
+    out = []
+    for e in range(d['E'] + (1 if d['shared'] else 0)):
+        if d['host'] is not None:
+            out.append(d['host'][e])
+        elif e in needed or e == d['E']:
+            out.append(tuple(w.numpy() for w in d['dev'][e]))
+        else:
+            out.append(None)
+    return out
+
+
+def check_layer(layer, d, x, tol=REL_TOL):
+    P, O = pkg(), oracle()
+    M = x.shape[0]
+    y, sel, wts = P.moe_forward(layer, torch.from_numpy(x).cuda())
+    torch.cuda.synchronize()
+    sel_h, wts_h = sel.cpu().numpy(), wts.cpu().numpy()
+    logits = O.router_logits(x, d['rb'])
+    sel_o, wts_o, gap = O.route(logits, d['bias'], d['topk'])
+    assert gap.min() > 1e-6, 'seed gives a near-tie in the ranking; pick another'
+    for m in range(M):
+        assert set(sel_h[m].tolist()) == set(sel_o[m].tolist()), m
+        ref = {int(e): float(w) for e, w in zip(sel_o[m], wts_o[m])}
+        assert all(abs(ref[int(e)] - float(w)) < 1e-5 for e, w in zip(sel_h[m], wts_h[m]))
+        assert list(sel_h[m]) == list(sel_o[m])        # and in the same (descending) order
+    ex = host_experts(d, set(sel_o.ravel().tolist()))
+    yo = O.moe_experts(x, sel_o, wts_o, ex[:d['E']], ex[d['E']] if d['shared'] else None)
+    r, a = O.rel_l2(y.cpu().numpy(), yo), O.max_abs(y.cpu().numpy(), yo)
+    assert r <= tol and a <= ABS_TOL, (r, a)
+    return y, sel, wts
+
+
+def test_moe_golden(golden):
+    P, O = pkg(), oracle()
+    z = golden('moe')
+    E, K, H, I = int(z['E']), int(z['topk']), int(z['H']), int(z['I'])
+    trip = lambda e, nm: P.Nvfp4Weight(z['e%d_%s_packed' % (e, nm)], z['e%d_%s_scale' % (e, nm)], z['e%d_%s_gs' % (e, nm)])
+    ex = [(trip(e, 'gate'), trip(e, 'up'), trip(e, 'down')) for e in range(E + 1)]
+    layer = P.MoeLayer(to_dev_bf16(z['router_bits']), torch.from_numpy(z['bias']).cuda(), ex[:E], ex[E], K, H, I,
+                       float(z['scaling']), float(z['limit']))
+    y, sel, wts = P.moe_forward(layer, torch.from_numpy(z['x']).cuda())
+    for m in range(int(z['M'])):
+        assert set(sel[m].tolist()) == set(z['sel'][m].tolist())
+        ref = {int(e): float(w) for e, w in zip(z['sel'][m], z['wts'][m])}
+        assert all(abs(ref[int(e)] - float(w)) < 1e-5 for e, w in zip(sel[m].tolist(), wts[m].tolist()))
+        # row 2 saturates the SwiGLU clamps and is 40x larger: judge each row on its own norm
+        assert O.rel_l2(y[m].cpu().numpy(), z['y'][m]) <= REL_TOL, m
+
+
+@pytest.mark.parametrize('M', [1, 4])
+@pytest.mark.parametrize('shared', [True, False])
+def test_moe_mid_geometry(M, shared):
+    layer, d = build_layer(1024, 512, 32, 8, seed=5, shared=shared)
+    x = np.random.default_rng(M).normal(0, 1, (M, 1024)).astype(np.float32)
+    check_layer(layer, d, x)
+
+
+@pytest.mark.parametrize('I', [1536, 2048])
+def test_moe_full_geometry(I):
+    """hidden 4096, 144 experts, top-8 + shared; inter 1536 (benchmark) and 2048 (reference)."""
+    layer, d = build_layer(4096, I, 144, 8, seed=40 + I, on_gpu=True)
+    x = np.random.default_rng(I).normal(0, 1, (4, 4096)).astype(np.float32)
+    y4, sel4, wts4 = check_layer(layer, d, x)
+    P = pkg()
+    # token m of a batch == that token alone, bit for bit (reference include/moe.h:38-40)
+    for m in range(4):
+        y1, sel1, wts1 = P.moe_forward(layer, torch.from_numpy(x[m:m + 1]).cuda())
+        assert torch.equal(y1[0], y4[m]) and torch.equal(sel1[0], sel4[m]) and torch.equal(wts1[0], wts4[m])
+    # expert half with the routing handed in == whole block
+    y = P.moe_experts(layer, torch.from_numpy(x).cuda(), sel4, wts4)
+    assert torch.equal(y, y4)
+    # run-to-run
+    y_again, _, _ = P.moe_forward(layer, torch.from_numpy(x).cuda())
+    assert torch.equal(y_again, y4)
+    if I == 2048:
+        R = ref_kernels()
+        if R is None:
+            pytest.skip('oracle/_ref/libref_kernels.so was not prebuilt')
+        assert (R.ref_moe_hidden(), R.ref_moe_inter(), R.ref_moe_experts(), R.ref_moe_topk()) == (4096, 2048, 144, 8)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        for M in (1, 4):
+            xd = torch.from_numpy(x[:M]).cuda()
+            ws = torch.zeros(R.ref_moe_workspace_floats(M), dtype=torch.float32, device='cuda')
+            yr = torch.zeros((M, 4096), device='cuda'); selr = torch.zeros((M, 8), dtype=torch.int32, device='cuda')
+            wtsr = torch.zeros((M, 8), device='cuda')
+            R.ref_moe_forward(p(xd), p(layer.router), p(layer.bias), p(layer.table), p(layer.shared_table), 144, 8,
+                              p(yr), p(selr), p(wtsr), p(ws), M, None)
+            torch.cuda.synchronize()
+            assert torch.equal(selr, sel4[:M])
+            assert (wtsr - wts4[:M]).abs().max().item() < 1e-5
+            O = oracle()
+            assert O.rel_l2(y4[:M].cpu().numpy(), yr.cpu().numpy()) <= REL_TOL
+
+
+def test_route_ties_lowest_index_wins():
+    """Two experts with identical router rows and biases tie exactly; the lower index must be
+    ranked first (reference kernels/moe.cu:146-152)."""
+    P, O = pkg(), oracle()
+    H, E, K = 256, 40, 4
+    rng = np.random.default_rng(1)
+    w = rng.normal(0, 0.05, (E, H)).astype(np.float32)
+    w[33] = w[2]; w[17] = w[2]
+    rb = O.f32_to_bf16_bits(w)
+    bias = np.zeros(E, np.float32)
+    x = rng.normal(0, 1, (3, H)).astype(np.float32)
+    x[0] = w[2] * 40                                    # make the tied experts the top choice
+    dummy = P.Nvfp4Weight(*host_triple((32, 32), 1))
+    layer = P.MoeLayer(to_dev_bf16(rb), torch.from_numpy(bias).cuda(), [(dummy, dummy, dummy)] * E, None, K, H, 32)
+    sel, wts, logits = P.moe_route(layer, torch.from_numpy(x).cuda())
+    lo = O.router_logits(x, rb)
+    assert O.rel_l2(logits.cpu().numpy(), lo) < 1e-5
+    so, wo, _ = O.route(logits.cpu().numpy().astype(np.float64), bias, K)
+    assert np.array_equal(sel.cpu().numpy(), so)
+    assert list(sel[0, :3].tolist()) == [2, 17, 33]
+    assert np.abs(wts.cpu().numpy() - wo).max() < 1e-5

@@ -1,0 +1,295 @@
+"""GPU parity: every CUDA entry point, called through the C ABI, against the CPU oracle.
+
+Bar: codes, scales and global scales bit-exact; gemv / gemm / MoE outputs within rel-L2 1e-3 and
+max-abs 2e-2 of an fp64-accumulated dequant-then-matmul; expert selection identical as a set,
+gate weights within 1e-5.  Structural checks follow the reference's own gates
+(tests/gate_nvfp4.cu:114-125, tests/gate_gemv_multi.cu:104-128): a gemm row equals the gemv of
+that row bit for bit, a fused group equals its separate gemvs bit for bit, outputs are
+poison-filled first, and an all-zero result does not count as agreement.
+"""
+import ctypes as C
+import numpy as np
+import pytest
+import torch
+
+from util import (pkg, oracle, seeded_bf16, host_triple, to_dev_bf16, ref_kernels, REL_TOL, ABS_TOL)
+
+pytestmark = pytest.mark.gpu
+
+
+def dev_weight(t):
+    return pkg().Nvfp4Weight(*t)
+
+
+def close(y, ref):
+    O = oracle()
+    r, a = O.rel_l2(y, ref), O.max_abs(y, ref)
+    assert r <= REL_TOL and a <= ABS_TOL, (r, a)
+    assert np.abs(np.asarray(ref)).max() > 0
+    return r
+
+
+# ---- quantiser ---------------------------------------------------------------------------------
+
+def _quant_case(bits):
+    P, O = pkg(), oracle()
+    W = P.quantize(to_dev_bf16(bits))
+    torch.cuda.synchronize()
+    p, s, gs = O.quantize_tensor(O.bf16_bits_to_f32(bits))
+    gp, gsc, ggs = W.numpy()
+    assert ggs.view(np.uint32)[0] == gs.view(np.uint32)[0]
+    assert np.array_equal(gsc, s)
+    assert np.array_equal(gp, p)
+    return W, (p, s, gs)
+
+
+def test_quantize_golden_bit_exact(golden):
+    for name, tags in (('quant_normal', ['w%d' % i for i in range(5)]), ('quant_edges', list('abcde'))):
+        z = golden(name)
+        for t in tags:
+            W, _ = _quant_case(z[t + '_bits'])
+            gp, gsc, ggs = W.numpy()
+            assert np.array_equal(gp, z[t + '_packed']) and np.array_equal(gsc, z[t + '_scale']), t
+            assert ggs.view(np.uint32)[0] == z[t + '_gs'].view(np.uint32)[0], t
+            d = pkg().dequantize(W).cpu().numpy()
+            assert np.array_equal(d.view(np.uint32), z[t + '_deq'].view(np.uint32)), t
+
+
+@pytest.mark.parametrize('shape', [(1, 16), (3, 48), (257, 1536), (1024, 4096), (0, 64)])
+def test_quantize_random_bit_exact(shape):
+    _quant_case(seeded_bf16(shape, 11 + shape[0]))
+
+
+def test_quantize_wide_range_and_unaligned():
+    rng = np.random.default_rng(5)
+    w = (np.exp(rng.uniform(-20, 8, (64, 512))) * rng.choice([-1.0, 1.0], (64, 512))).astype(np.float32)
+    w[rng.random((64, 512)) < 0.1] = 0.0
+    bits = oracle().f32_to_bf16_bits(w)
+    _quant_case(bits)
+    # an input that starts 2 bytes past a 16-byte boundary takes the scalar load path
+    P, O = pkg(), oracle()
+    buf = torch.zeros(64 * 512 + 1, dtype=torch.bfloat16, device='cuda')
+    buf[1:] = to_dev_bf16(bits).reshape(-1)
+    W = P.quantize(buf[1:].view(64, 512))
+    p, s, gs = O.quantize_tensor(O.bf16_bits_to_f32(bits))
+    gp, gsc, ggs = W.numpy()
+    assert np.array_equal(gp, p) and np.array_equal(gsc, s) and ggs[0] == gs[0]
+
+
+def test_quantize_with_given_scale():
+    P, O = pkg(), oracle()
+    bits = seeded_bf16((32, 256), 3, std=1.0)
+    gs = np.array([37.5], np.float32)
+    W = P.quantize(to_dev_bf16(bits), gscale_in=torch.from_numpy(gs).cuda())
+    p, s = O.quantize(O.bf16_bits_to_f32(bits), gs[0])
+    assert np.array_equal(W.packed.cpu().numpy(), p) and np.array_equal(W.scale.cpu().numpy(), s)
+
+
+def test_quantize_full_size_properties():
+    """[12288 x 4096]: compared in full with the C oracle, plus the round-trip error band the
+    reference records for this format (rel 0.088-0.100)."""
+    import ctypes as C
+    from util import c_oracle
+    P, O = pkg(), oracle()
+    bits = seeded_bf16((12288, 4096), 1000)
+    W = P.quantize(to_dev_bf16(bits))
+    L = c_oracle()
+    gs = L.oracle_global_scale(bits.ctypes.data_as(C.c_void_p), bits.size)
+    p = np.zeros((12288, 2048), np.uint8); s = np.zeros((12288, 256), np.uint8)
+    L.oracle_quantize(bits.ctypes.data_as(C.c_void_p), 12288, 4096, C.c_float(gs), p.ctypes.data_as(C.c_void_p),
+                      s.ctypes.data_as(C.c_void_p))
+    gp, gsc, ggs = W.numpy()
+    assert ggs[0] == np.float32(gs) and np.array_equal(gsc, s) and np.array_equal(gp, p)
+    d = P.dequantize(W)
+    w = to_dev_bf16(bits).float()
+    rel = ((d - w).norm() / w.norm()).item()
+    assert 0.085 < rel < 0.102, rel
+
+
+# ---- gemv / gemm -------------------------------------------------------------------------------
+
+GEMV_SHAPES = [(1, 96, 512), (1, 1, 32), (1, 5, 128), (2, 33, 1536), (3, 70, 4096), (4, 130, 1024),
+               (5, 64, 2048), (6, 40, 96), (7, 17, 4096), (8, 257, 1536), (1, 300, 12288), (8, 64, 12288),
+               (1, 9, 16), (4, 21, 48), (8, 12, 80)]           # the last three take the generic kernel
+
+
+@pytest.mark.parametrize('M,N,K', GEMV_SHAPES)
+def test_gemm_vs_oracle(M, N, K):
+    P, O = pkg(), oracle()
+    t = host_triple((N, K), 100 + N + K)
+    x = np.random.default_rng(7 + M).normal(0, 1, (M, K)).astype(np.float32)
+    y = torch.full((M, N), float('nan'), device='cuda')
+    P.gemm(dev_weight(t), torch.from_numpy(x).cuda(), y)
+    close(y.cpu().numpy(), O.gemm(x, *t))
+
+
+def test_gemv_golden(golden):
+    z = golden('gemv')
+    for i in range(3):
+        t = (z['g%d_packed' % i], z['g%d_scale' % i], z['g%d_gs' % i])
+        y = pkg().gemm(dev_weight(t), torch.from_numpy(z['g%d_x' % i]).cuda()).cpu().numpy()
+        close(y, z['g%d_y' % i])
+
+
+def test_gemm_large_M_chunks():
+    P, O = pkg(), oracle()
+    t = host_triple((48, 512), 5)
+    x = np.random.default_rng(8).normal(0, 1, (19, 512)).astype(np.float32)
+    W = dev_weight(t)
+    y = P.gemm(W, torch.from_numpy(x).cuda())
+    close(y.cpu().numpy(), O.gemm(x, *t))
+    for m in (0, 7, 8, 18):
+        assert torch.equal(P.gemm(W, torch.from_numpy(x[m:m + 1]).cuda())[0], y[m])
+
+
+def test_gemm_rows_equal_gemv_bitwise():
+    P = pkg()
+    for (N, K) in [(300, 4096), (64, 1536), (33, 128)]:
+        W = dev_weight(host_triple((N, K), N))
+        x = torch.from_numpy(np.random.default_rng(N).normal(0, 1, (8, K)).astype(np.float32)).cuda()
+        for M in (1, 2, 3, 4, 5, 8):
+            y = P.gemm(W, x[:M].contiguous())
+            for m in range(M):
+                ym = P.gemm(W, x[m:m + 1].contiguous())
+                assert torch.equal(y[m], ym[0]), (N, K, M, m)
+            assert (y != 0).float().mean() > 0.5
+
+
+def test_gemv_run_to_run_identical():
+    P = pkg()
+    W = dev_weight(host_triple((1000, 4096), 1))
+    x = torch.randn(1, 4096, device='cuda')
+    a = P.gemm(W, x)
+    for _ in range(3):
+        assert torch.equal(P.gemm(W, x), a)
+
+
+def test_gemv_extreme_activation_ranges():
+    """The fp16 staging is scaled per row, so huge, tiny and zero rows must all stay exact to
+    the same relative tolerance."""
+    P, O = pkg(), oracle()
+    t = host_triple((64, 1024), 21)
+    rng = np.random.default_rng(3)
+    x = rng.normal(0, 1, (4, 1024)).astype(np.float32)
+    x[0] *= 1e6; x[1] *= 1e-6; x[2] = 0.0; x[3, ::2] *= 1e-4
+    y = P.gemm(dev_weight(t), torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = O.gemm(x, *t)
+    for m in (0, 1, 3):
+        assert O.rel_l2(y[m], ref[m]) <= REL_TOL, m
+    assert np.all(y[2] == 0)
+
+
+def test_gemv_unaligned_tensors_take_generic_path():
+    P, O = pkg(), oracle()
+    p, s, gs = host_triple((40, 256), 2)
+    x = np.random.default_rng(1).normal(0, 1, (2, 256)).astype(np.float32)
+    buf = torch.zeros(p.size + 4, dtype=torch.uint8, device='cuda')
+    buf[4:] = torch.from_numpy(p).cuda().reshape(-1)            # 4-byte aligned only
+    sbuf = torch.zeros(s.size + 1, dtype=torch.uint8, device='cuda')
+    sbuf[1:] = torch.from_numpy(s).cuda().reshape(-1)           # odd address
+    W = P.Nvfp4Weight(buf[4:].view(40, 128), sbuf[1:].view(40, 16), torch.from_numpy(gs).cuda())
+    y = P.gemm(W, torch.from_numpy(x).cuda()).cpu().numpy()
+    close(y, O.gemm(x, p, s, gs))
+
+
+def test_dense_bf16_f32_gemm():
+    P, O = pkg(), oracle()
+    rng = np.random.default_rng(4)
+    for (M, N, K) in [(1, 144, 4096), (4, 144, 4096), (3, 10, 100), (9, 7, 64)]:
+        w = rng.normal(0, 0.02, (N, K)).astype(np.float32)
+        x = rng.normal(0, 1, (M, K)).astype(np.float32)
+        wb = O.f32_to_bf16_bits(w)
+        y = P.gemm(to_dev_bf16(wb), torch.from_numpy(x).cuda()).cpu().numpy()
+        ref = x.astype(np.float64) @ O.bf16_bits_to_f32(wb).astype(np.float64).T
+        assert O.rel_l2(y, ref) < 1e-5
+        y = P.gemm(torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()).cpu().numpy()
+        assert O.rel_l2(y, x.astype(np.float64) @ w.astype(np.float64).T) < 1e-5
+
+
+def test_converters():
+    P = pkg()
+    x = torch.randn(1000, device='cuda')
+    b = P.f32_to_bf16(x)
+    assert torch.equal(b, x.to(torch.bfloat16))
+    assert torch.equal(P.bf16_to_f32(b), b.float())
+
+
+# ---- fused sibling gemvs -------------------------------------------------------------------------
+
+SIBLINGS = [4096, 4096, 4096, 512, 64, 32]
+
+
+@pytest.mark.parametrize('M', [1, 2, 4, 8])
+def test_gemv_multi_siblings(M):
+    """Six weights sharing one input, K = 4096: one launch, bit-identical to six separate calls,
+    and within tolerance of the oracle."""
+    P, O = pkg(), oracle()
+    K = 4096
+    ts = [host_triple((n, K), 1000 + i) for i, n in enumerate(SIBLINGS)]
+    Ws = [dev_weight(t) for t in ts]
+    xh = np.random.default_rng(2).normal(0, 1, (M, K)).astype(np.float32)
+    x = torch.from_numpy(xh).cuda()
+    ys = [torch.full((M, n), float('nan'), device='cuda') for n in SIBLINGS]
+    P.gemv_multi(Ws, x, M, ys)
+    for W, t, y in zip(Ws, ts, ys):
+        sep = torch.full_like(y, float('inf'))
+        P.gemm(W, x, sep)
+        assert torch.equal(sep, y)
+        close(y.cpu().numpy(), O.gemm(xh, *t))
+
+
+def test_gemv_multi_per_job_inputs_and_ragged():
+    P, O = pkg(), oracle()
+    K = 128
+    shapes = [130, 7, 64]
+    ts = [host_triple((n, K), 50 + i) for i, n in enumerate(shapes)]
+    Ws = [dev_weight(t) for t in ts]
+    xs_h = [np.random.default_rng(60 + i).normal(0, 1, (1, K)).astype(np.float32) for i in range(3)]
+    xs = [torch.from_numpy(a).cuda() for a in xs_h]
+    ys = P.gemv_multi(Ws, xs, 1)
+    for W, t, xh, x, y in zip(Ws, ts, xs_h, xs, ys):
+        assert torch.equal(P.gemm(W, x), y)
+        close(y.cpu().numpy(), O.gemm(xh, *t))
+
+
+def test_gemv_multi_eight_jobs():
+    P = pkg()
+    K = 512
+    Ws = [dev_weight(host_triple((16 + 9 * i, K), 70 + i)) for i in range(8)]
+    x = torch.randn(2, K, device='cuda')
+    ys = P.gemv_multi(Ws, x, 2)
+    for W, y in zip(Ws, ys):
+        assert torch.equal(P.gemm(W, x), y)
+
+
+def test_error_codes_on_device_pointers():
+    P = pkg()
+    W = dev_weight(host_triple((8, 32), 1))
+    x = torch.randn(1, 40, device='cuda')
+    y = torch.empty(1, 8, device='cuda')
+    ref = W.wref()
+    rc = P.lib().b200_nvfp4_gemm(C.c_void_p(y.data_ptr()), C.byref(ref), C.c_void_p(x.data_ptr()), 1, 8, 40, 1, None)
+    assert rc == 2
+    with pytest.raises(P.B200Error):
+        P.check(rc, 'gemm')
+
+
+# ---- against the reference's own kernels on the same buffers ---------------------------------------
+
+def test_gemv_vs_reference_kernel():
+    R = ref_kernels()
+    if R is None:
+        pytest.skip('oracle/_ref/libref_kernels.so was not prebuilt')
+    P, O = pkg(), oracle()
+    for (M, N, K) in [(1, 1000, 4096), (4, 333, 1536), (1, 64, 128)]:
+        W = dev_weight(host_triple((N, K), N + K))
+        x = torch.randn(M, K, device='cuda')
+        y = P.gemm(W, x)
+        yr = torch.zeros_like(y)
+        R.ref_gemm_nvfp4(y_ptr(yr), y_ptr(W.packed), y_ptr(W.scale), y_ptr(W.gscale), y_ptr(x), M, N, K, None)
+        torch.cuda.synchronize()
+        close(y.cpu().numpy(), yr.cpu().numpy())
+
+
+def y_ptr(t):
+    return C.c_void_p(t.data_ptr())
