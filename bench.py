@@ -95,26 +95,37 @@ def nv_bytes(N, K):
     return N * K // 2 + N * K // 16 + 4
 
 
-def time_graphs(graphs, steps, warmup, sampler=None):
-    """Replays one captured step per call, cycling over `graphs`; device time per step in ms."""
-    for i in range(warmup):
-        graphs[i % len(graphs)].replay()
+def capture_steps(fns):
+    """One CUDA graph holding the given steps back to back (kernel nodes keep the programmatic
+    launch edges the library asks for, so consecutive steps overlap their ramp and tail)."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for fn in fns:
+            fn()
+    return g
+
+
+def time_steps(fns, steps, warmup):
+    """Runs exactly `steps` timed steps, step i being fns[i % len(fns)]: whole rotations as one
+    captured graph each, plus one shorter graph for the remainder.  Returns ms per step."""
+    for fn in fns:
+        fn()                                        # outside capture: one-time attribute set-up
+    torch.cuda.synchronize()
+    R = len(fns)
+    full = capture_steps(fns)
+    rem = capture_steps(fns[:steps % R]) if steps % R else None
+    for _ in range(max(1, (warmup + R - 1) // R)):
+        full.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        graphs[i % len(graphs)].replay()
+    for _ in range(steps // R):
+        full.replay()
+    if rem is not None:
+        rem.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
-
-
-def capture(fn):
-    g = torch.cuda.CUDAGraph()
-    fn(); torch.cuda.synchronize()                 # first call outside capture: attribute set-up
-    with torch.cuda.graph(g):
-        fn()
-    return g
 
 
 def make_weight(P, N, K, seed):
@@ -135,15 +146,15 @@ def bench_siblings(P, M, steps, warmup, copies, sampler_index=None):
     x = torch.randn((M, K_HID), device='cuda', generator=torch.Generator(device='cuda').manual_seed(2))
     ys = [torch.empty((M, n), device='cuda') for n in SIBLINGS]
     jobs = [P.make_jobs(ws, [x] * 6, ys) for ws in sets]
-    graphs = [capture(lambda ws=ws, j=j: P.gemv_multi(ws, x, M, ys, jobs=j)) for ws, j in zip(sets, jobs)]
+    fns = [lambda ws=ws, j=j: P.gemv_multi(ws, x, M, ys, jobs=j) for ws, j in zip(sets, jobs)]
     nbytes = sum(nv_bytes(n, K_HID) for n in SIBLINGS) + M * K_HID * 4 + M * sum(SIBLINGS) * 4
     if sampler_index is None:
-        ms = time_graphs(graphs, steps, warmup)
+        ms = time_steps(fns, steps, warmup)
         return ms, nbytes, None, (sets, x, ys, jobs)
     with ClockSampler(sampler_index) as cs:
-        ms = time_graphs(graphs, steps, warmup)
+        ms = time_steps(fns, steps, warmup)
         if steps * ms < 400:                        # keep the region long enough to be sampled
-            time_graphs(graphs, int(400 / max(ms, 1e-3)), 0)
+            time_steps(fns, int(400 / max(ms, 1e-3)), 0)
     return ms, nbytes, cs.summary(), (sets, x, ys, jobs)
 
 
@@ -178,8 +189,7 @@ def bench_gemv_single(P, steps, warmup, copies):
     ws = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
     x = torch.randn((1, K_HID), device='cuda')
     y = torch.empty((1, N), device='cuda')
-    graphs = [capture(lambda W=W: P.gemm(W, x, y)) for W in ws]
-    ms = time_graphs(graphs, steps, warmup)
+    ms = time_steps([lambda W=W: P.gemm(W, x, y) for W in ws], steps, warmup)
     return ms, nv_bytes(N, K_HID) + K_HID * 4 + N * 4
 
 
@@ -207,12 +217,12 @@ def bench_moe(P, layers, M, steps, warmup):
     y = torch.empty((M, H), device='cuda'); sel = torch.empty((M, topk), dtype=torch.int32, device='cuda')
     wts = torch.empty((M, topk), device='cuda')
     combos = [(layers[i % len(layers)], xs[i % len(xs)]) for i in range(max(len(layers), len(xs)))]
-    graphs, distinct = [], []
+    fns, distinct = [], []
     for L, x in combos:
-        graphs.append(capture(lambda L=L, x=x: P.moe_forward(L, x, y, sel, wts)))
-        torch.cuda.synchronize()
+        fns.append(lambda L=L, x=x: P.moe_forward(L, x, y, sel, wts))
+        fns[-1](); torch.cuda.synchronize()
         distinct.append(len(set(sel.cpu().numpy().ravel().tolist())))
-    ms = time_graphs(graphs, steps, warmup)
+    ms = time_steps(fns, steps, warmup)
     per_expert = 3 * nv_bytes(I, H)
     d = float(np.mean(distinct))
     nbytes = (d + 1) * per_expert + E * H * 2 + E * 4 + 2 * M * H * 4 + M * topk * 8
@@ -223,8 +233,7 @@ def bench_quantize(P, steps, warmup):
     N, K = 12288, K_HID
     ws = [(torch.randn((N, K), device='cuda') * 0.02).to(torch.bfloat16) for _ in range(3)]
     out = P.quantize(ws[0])
-    graphs = [capture(lambda w=w: P.quantize(w, out=out)) for w in ws]
-    ms = time_graphs(graphs, steps, warmup)
+    ms = time_steps([lambda w=w: P.quantize(w, out=out) for w in ws], steps, warmup)
     # two passes over the bf16 input (tensor amax, then codes) plus the NVFP4 output
     return ms, 2 * N * K * 2 + nv_bytes(N, K)
 
@@ -286,6 +295,7 @@ def main():
         raise SystemExit('bench.py needs a CUDA device: there is no CPU fallback')
     torch.cuda.set_device(local)
     P.lib()                                            # fail now if the library is missing
+    P.set_option(P.OPT_STABLE_WEIGHTS, 1)              # weights are loaded once, as in the engine
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group('nccl', device_id=torch.device('cuda', local))
@@ -329,6 +339,7 @@ def main():
         'data': 'synthetic',
         'config': {'workload': 'six fused sibling NVFP4 gemvs sharing one input, K=4096, N=[4096,4096,4096,512,64,32], M=1 (configs[1])',
                    'l2': 'inputs larger than L2: step i reads weight copy i mod %d (%.0f MB in rotation)' % (copies, copies * nbytes / 1e6),
+                   'launch': 'steps captured back to back in CUDA graphs; programmatic dependent launch; weights declared stable',
                    'math': 'fp32-mac' if P.lib() and os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'},
         'roofline': {'bound': 'hbm', 'kernel': 'k_gemv_nvfp4<1,4>', 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
                      'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': None,

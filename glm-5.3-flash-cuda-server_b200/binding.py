@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, 'libb200nvfp4.so')
+LIB_PATH = os.environ.get('B200_NVFP4_LIB') or os.path.join(_HERE, 'libb200nvfp4.so')
 _lib = None
 
 F32, BF16 = 0, 1
@@ -50,6 +50,7 @@ def lib():
         vp, ci, st = C.c_void_p, C.c_int, C.c_size_t
         L.b200_nvfp4_strerror.restype = C.c_char_p; L.b200_nvfp4_strerror.argtypes = [ci]
         L.b200_nvfp4_version.restype = ci
+        L.b200_nvfp4_device_status.argtypes = [C.POINTER(C.c_uint), ci]
         L.b200_nvfp4_gemm.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp]
         L.b200_nvfp4_gemv_multi.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp]
         L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
@@ -64,7 +65,7 @@ def lib():
     return _lib
 
 
-EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
+EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
            'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts']
 
@@ -72,6 +73,20 @@ EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_gemm', 'b200
 def check(rc, what):
     if rc != 0:
         raise B200Error('%s failed: %s (%d)' % (what, lib().b200_nvfp4_strerror(rc).decode(), rc))
+
+
+def device_status(clear=False):
+    """0 unless a bounded wait inside a kernel ever ran out (synchronises the device)."""
+    v = C.c_uint(0)
+    check(lib().b200_nvfp4_device_status(C.byref(v), 1 if clear else 0), 'b200_nvfp4_device_status')
+    return v.value
+
+
+OPT_STABLE_WEIGHTS = 1
+
+
+def set_option(option, value):
+    check(lib().b200_nvfp4_set_option(int(option), int(value)), 'b200_nvfp4_set_option')
 
 
 def stream_ptr(stream=None):

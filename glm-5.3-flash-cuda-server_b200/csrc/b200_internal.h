@@ -13,10 +13,29 @@ int sm_count();
 // cudaGetLastError() after a launch: 0, or B200_ELAUNCH with the runtime's text on stderr.
 int check_launch(const char* what);
 int launch_failed(const char* what);
+// Device address of the status word that bounded waits write to (null if the query failed).
+unsigned int* device_status_ptr();
+// 1 if the caller declared weight buffers immutable while kernels run (B200_OPT_STABLE_WEIGHTS).
+int stable_weights_option();
+
+// One launch's worth of NVFP4 gemv jobs as the kernels see them.  task0 is the index of the
+// job's first row tile in the launch's flat tile list (general kernel only).
+struct GemvJobDev {
+    float* y; const uint8_t* P; const uint8_t* S; const float* gs; const float* x;
+    int N; int task0;
+};
+struct GemvParams {
+    GemvJobDev j[B200_GEMV_MULTI_MAX];
+    int n_jobs, total_tasks, K;
+};
 
 // gemv.cu
 int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s);
 int dense_gemm(float* y, const void* W, const float* x, int M, int N, int K, int dtype, cudaStream_t s);
 int nvfp4_math_mode();
+
+// gemv_tma.cu: single-row (M = 1) bulk-copy pipelined kernel; returns B200_ENOTIMPL when the
+// shapes / alignments it needs do not hold, and the caller then uses the general kernel.
+int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
 
 }  // namespace b200

@@ -1,6 +1,7 @@
 // common.cu -- error reporting and cached device attributes.
 #include "b200_internal.h"
 #include <cstdio>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -15,6 +16,32 @@ int sm_count() {
     }
     return cache[dev];
 }
+
+// Written by a kernel whose bounded wait ran out (see tma_pipe.cuh); read by
+// b200_nvfp4_device_status.  One word per device that loads the library.
+__device__ unsigned int g_device_status = 0;
+
+unsigned int* device_status_ptr() {
+    static unsigned int* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<unsigned int*>(p);
+    }
+    return cache[dev];
+}
+
+static int g_stable_weights = -1;
+int stable_weights_option() {
+    if (g_stable_weights < 0) {
+        const char* e = getenv("B200_STABLE_WEIGHTS");
+        g_stable_weights = (e && *e == '1') ? 1 : 0;
+    }
+    return g_stable_weights;
+}
+void set_stable_weights(int v) { g_stable_weights = v ? 1 : 0; }
 
 int launch_failed(const char* what) {
     const cudaError_t e = cudaGetLastError();
@@ -45,3 +72,18 @@ extern "C" const char* b200_nvfp4_strerror(int code) {
 }
 
 extern "C" int b200_nvfp4_version(void) { return 100; }
+
+extern "C" int b200_nvfp4_set_option(int option, int value) {
+    if (option != B200_OPT_STABLE_WEIGHTS) return B200_EINVAL;
+    b200::set_stable_weights(value);
+    return B200_OK;
+}
+
+extern "C" int b200_nvfp4_device_status(unsigned int* out, int clear) {
+    if (!out) return B200_EINVAL;
+    unsigned int* p = b200::device_status_ptr();
+    if (!p) return B200_ELAUNCH;
+    if (cudaMemcpy(out, p, sizeof(*out), cudaMemcpyDeviceToHost) != cudaSuccess) return b200::launch_failed("device_status read");
+    if (clear && *out && cudaMemset(p, 0, sizeof(*out)) != cudaSuccess) return b200::launch_failed("device_status clear");
+    return B200_OK;
+}

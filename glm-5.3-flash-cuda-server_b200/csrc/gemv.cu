@@ -21,15 +21,6 @@
 
 namespace b200 {
 
-struct GemvJobDev {
-    float* y; const uint8_t* P; const uint8_t* S; const float* gs; const float* x;
-    int N; int task0;
-};
-struct GemvParams {
-    GemvJobDev j[B200_GEMV_MULTI_MAX];
-    int n_jobs, total_tasks, K;
-};
-
 template <int M, int R, int MATH>
 __global__ void __launch_bounds__(GEMV_THREADS)
 k_gemv_nvfp4(const __grid_constant__ GemvParams p) {
@@ -232,6 +223,13 @@ static int launch_m(const GemvParams& p, bool fast, size_t smem, cudaStream_t s)
     return nvfp4_math_mode() ? launch_fast<M, 1>(p, smem, s) : launch_fast<M, 0>(p, smem, s);
 }
 
+// B200_NVFP4_GENERAL=1 keeps every shape on the general kernel (used by tests that compare the
+// two kernels bit for bit, and for profiling).
+static bool force_general() {
+    const char* e = getenv("B200_NVFP4_GENERAL");
+    return e && *e == '1';
+}
+
 int rows_per_tile(int M) { return GEMV_WARPS * (M <= 2 ? 4 : 2); }
 
 // Validates, decides fast vs generic, builds the flat task list, launches.  n in 1..8, M in 1..8.
@@ -255,6 +253,10 @@ int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s) 
     }
     for (int i = n; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].N = 0; p.j[i].task0 = 0x7fffffff; }
     p.total_tasks = tasks;
+    if (M == 1 && fast && !force_general()) {
+        const int rc = nvfp4_multi_tma(p, s);
+        if (rc != B200_ENOTIMPL) return rc;
+    }
     switch (M) {
         case 1: return launch_m<1>(p, fast, smem, s);
         case 2: return launch_m<2>(p, fast, smem, s);

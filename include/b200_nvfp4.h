@@ -78,6 +78,23 @@ typedef struct {
 const char* b200_nvfp4_strerror(int code);
 int         b200_nvfp4_version(void);
 
+/* Every wait inside a kernel of this library is bounded.  If one ever runs out, the kernel
+ * records (site << 16 | block) in a per-device status word and carries on to termination; the
+ * outputs of that launch are then undefined.  This call SYNCHRONISES the device copy of that
+ * word into *out (host pointer; 0 = nothing happened) and optionally clears it.  No counterpart
+ * in the reference, whose kernels never wait on one another. */
+int b200_nvfp4_device_status(unsigned int* out, int clear);
+
+/* Process-wide options.  B200_OPT_STABLE_WEIGHTS = 1 declares that no kernel running on a
+ * stream writes NVFP4 weight buffers that a later call on that stream reads (true for an
+ * inference engine, whose weights are loaded once).  The pipelined kernels, which are launched
+ * with programmatic stream serialisation, may then start copying weights while the previous
+ * kernel of the stream is still finishing; activations, scales and outputs are still only
+ * touched after the previous kernel has completed.  Default 0 (also settable with the
+ * environment variable B200_STABLE_WEIGHTS=1).  No counterpart in the reference. */
+enum { B200_OPT_STABLE_WEIGHTS = 1 };
+int b200_nvfp4_set_option(int option, int value);
+
 /* y[M,N] = x[M,K] . W[N,K]^T.  Replaces glm5::gemm / glm5::gemv (reference include/gemv.h:29,
  * 75; kernels/gemv.cu:369-396, 456-465, 649-701).  Any M >= 1: rows are processed in chunks of
  * up to 8 and W is re-read once per chunk.  Each output row of y depends only on its own row

@@ -155,6 +155,24 @@ def test_gemm_rows_equal_gemv_bitwise():
             assert (y != 0).float().mean() > 0.5
 
 
+def test_pipelined_and_general_kernels_agree_bitwise(monkeypatch):
+    """M = 1 with K % 256 == 0 runs the bulk-copy pipelined kernel; everything else runs the
+    general kernel.  Both must give the same bits, or a gemm row would differ from its gemv."""
+    P = pkg()
+    for (N, K) in [(12288, 4096), (1000, 4096), (700, 1536), (515, 256), (4096, 2048)]:
+        W = dev_weight(host_triple((min(N, 1024), K), N + K)) if N <= 1024 else P.quantize(
+            (torch.randn((N, K), device='cuda') * 0.02).to(torch.bfloat16))
+        x = torch.randn(1, K, device='cuda')
+        monkeypatch.setenv('B200_NVFP4_GENERAL', '1')
+        a = P.gemm(W, x)
+        monkeypatch.setenv('B200_NVFP4_GENERAL', '0')
+        b = torch.full_like(a, float('nan'))
+        P.gemm(W, x, b)
+        assert torch.equal(a, b), (N, K)
+        assert (a != 0).float().mean() > 0.9
+    assert P.device_status() == 0
+
+
 def test_gemv_run_to_run_identical():
     P = pkg()
     W = dev_weight(host_triple((1000, 4096), 1))
