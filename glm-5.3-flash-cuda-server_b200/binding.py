@@ -61,13 +61,16 @@ def lib():
         L.b200_moe_route.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, ci, vp]
         L.b200_moe_forward.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
         L.b200_moe_experts.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
+        L.b200_moe_forward_static.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, ci, vp]
+        L.b200_moe_static_ws_limit.restype = st
         _lib = L
     return _lib
 
 
 EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
            'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
-           'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts']
+           'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
+           'b200_moe_forward_static', 'b200_moe_static_ws_limit']
 
 
 def check(rc, what):
@@ -252,3 +255,16 @@ def moe_experts(layer, x, sel, wts, y=None, stream=None):
     ws = layer.workspace(M)
     check(lib().b200_moe_experts(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), _ptr(ws), M, stream_ptr(stream)), 'b200_moe_experts')
     return y
+
+
+def moe_forward_static(layer, x, y=None, sel=None, wts=None, stream=None):
+    """moe_forward through the library's built-in scratch (no workspace tensor is created here)."""
+    x2 = x if x.dim() == 2 else x.unsqueeze(0)
+    M = x2.shape[0]
+    dev = x.device
+    y = torch.empty((M, layer.hidden), dtype=torch.float32, device=dev) if y is None else y
+    sel = torch.empty((M, layer.topk), dtype=torch.int32, device=dev) if sel is None else sel
+    wts = torch.empty((M, layer.topk), dtype=torch.float32, device=dev) if wts is None else wts
+    check(lib().b200_moe_forward_static(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), M, stream_ptr(stream)),
+          'b200_moe_forward_static')
+    return y, sel, wts

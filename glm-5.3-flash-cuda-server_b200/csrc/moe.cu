@@ -266,3 +266,60 @@ extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* 
     if (int rc = b200_moe_route(x, L, sel, wts, logits, M, stream)) return rc;
     return b200_moe_experts(x, L, y, sel, wts, ws, M, stream);
 }
+
+// ---- allocation-free variant -------------------------------------------------------------------
+// b200_moe_forward needs a workspace (router logits + the experts' intermediate activations),
+// and normally the caller allocates it from b200_moe_workspace_bytes.  Some hosts of this
+// library cannot do that.  The reference engine sizes its one workspace buffer at start-up from
+// ITS moe_workspace_floats(); once this library sits behind the old header the engine may be
+// running with a buffer of the old size, and it has no moment at which it could get a new one:
+// the MoE block runs between decode steps, where a cudaMalloc would synchronise the device and
+// stall the token loop, and under stream capture an allocation is not legal at all.  For those
+// callers the scratch lives inside the library, in the array below, which every GPU that loads
+// the library holds until the process exits.
+//
+// Limit: B200_MOE_STATIC_WS_BYTES (1 MiB) -- enough for 8 tokens at the reference geometry
+// (144 experts, top-8 + shared, inter 2048: 74 304 B per token).  Larger requests are refused.
+// The array is shared by every call on the device and keeps the previous call's bytes.  Nothing
+// in it has to start at zero: every byte a launch reads was written earlier by the same call
+// (logits by the router launch, activations by the gate/up launch), so it is never cleared.
+// Two calls whose kernels overlap on the GPU (different streams without an ordering between
+// them) would write the same scratch at once and corrupt each other: order them.
+constexpr size_t B200_MOE_STATIC_WS_BYTES = 1u << 20;
+static __device__ __align__(256) unsigned char g_moe_static_ws[B200_MOE_STATIC_WS_BYTES];
+
+// Device address of the array for the CURRENT device.  In host code the array's name is only a
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static int moe_static_ws_ptr(void** out) {
+    static void* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return b200::launch_failed("moe_forward_static: cudaGetDevice");
+    if (!cache[dev]) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_moe_static_ws);
+        if (e != cudaSuccess || !ptr) {
+            fprintf(stderr, "b200_nvfp4: cudaGetSymbolAddress(static MoE workspace) failed: %s\n", cudaGetErrorString(e));
+            return B200_ELAUNCH;
+        }
+        cache[dev] = ptr;
+    }
+    *out = cache[dev];
+    return B200_OK;
+}
+
+extern "C" size_t b200_moe_static_ws_limit(void) { return B200_MOE_STATIC_WS_BYTES; }
+
+extern "C" int b200_moe_forward_static(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
+                                       float* wts, int M, b200_stream stream) {
+    if (int rc = check_layer(L, M)) return rc;
+    const size_t need = b200_moe_workspace_bytes(L, M);
+    if (need > B200_MOE_STATIC_WS_BYTES) {
+        fprintf(stderr, "b200_nvfp4: b200_moe_forward_static needs %zu bytes of scratch for M=%d, the built-in "
+                        "workspace holds %zu; use b200_moe_forward with a caller-allocated workspace\n",
+                need, M, B200_MOE_STATIC_WS_BYTES);
+        return B200_ELIMIT;
+    }
+    void* ws = nullptr;
+    if (int rc = moe_static_ws_ptr(&ws)) return rc;
+    return b200_moe_forward(x, L, y, sel, wts, ws, M, stream);
+}

@@ -142,6 +142,21 @@ int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t*
 int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
                      const float* wts, void* ws, int M, b200_stream stream);
 
+/* b200_moe_forward without a workspace argument, for hosts that cannot allocate one: an engine
+ * whose buffers were sized at start-up by the reference's own moe_workspace_floats(), and which
+ * may not call cudaMalloc later (it would synchronise the device in the middle of the token
+ * loop, and is illegal under stream capture).  The scratch is a 1 MiB array inside the library
+ * (b200_moe_static_ws_limit()), held by every GPU that loads the library until exit; a layer /
+ * M whose b200_moe_workspace_bytes exceeds it is refused with B200_ELIMIT.  The call allocates
+ * nothing.  The FIRST call on each device looks the array's device address up
+ * (cudaGetSymbolAddress) -- make that call before any stream capture.  All calls on a device
+ * share the array and it keeps the last call's contents; nothing in it needs clearing, but two
+ * calls that overlap on the GPU race on it, so keep them on one stream or order them.
+ * This entry point has no counterpart in the reference. */
+size_t b200_moe_static_ws_limit(void);
+int b200_moe_forward_static(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
+                            float* wts, int M, b200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif
