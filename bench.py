@@ -238,6 +238,95 @@ def bench_quantize(P, steps, warmup):
     return ms, 2 * N * K * 2 + nv_bytes(N, K)
 
 
+def zipf_bias(E, s=1.1, seed=4, strength=0.08):
+    """Expert popularity ~ Zipf(s) over a seeded permutation, applied as a ranking bias (the
+    benchmark asks for Zipf-skewed routing; the router itself stays the model's)."""
+    rng = np.random.default_rng(seed)
+    p = 1.0 / np.arange(1, E + 1) ** s
+    p = p[rng.permutation(E)]
+    return torch.from_numpy((strength * np.log(p / p.mean())).astype(np.float32))
+
+
+def bench_ep(P, a, rank, local, world, peak):
+    """Expert-parallel MoE (configs[4]): T tokens x hidden 4096, 144 experts sharded over the ranks,
+    top-8 + replicated shared expert, 3 stacked layers, x <- rmsnorm(x + y) between layers."""
+    import torch.distributed as dist
+    dev = torch.device('cuda', local)
+    T, Lyr, E, topk, H, I = a.ep_tokens, 3, 144, 8, 4096, 1536
+    Tl = T // world
+    pb = zipf_bias(E)
+    layers = [P.ep_gpu.RankLayer(50, l, E, topk, H, I, rank, world, dev, popularity_bias=pb) for l in range(Lyr)]
+    g = torch.Generator(device=dev).manual_seed(123)
+    x_all = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16).float()      # bf16-valued activations
+    x0 = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
+
+    def step(x):
+        nb = 0
+        for L in layers:
+            y, _, _ = L.forward(x)
+            nb += L.step_bytes(Tl)
+            x = x + y
+            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)
+        return x, nb
+    for _ in range(a.warmup):
+        step(x0)
+    torch.cuda.synchronize(); dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as cs:
+        e0.record()
+        nb = 0
+        for _ in range(a.steps):
+            _, nb = step(x0)
+        e1.record()
+        torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    b = torch.tensor([float(nb)], device=dev, dtype=torch.float64)
+    dist.all_reduce(b)
+    ms = t.item() / a.steps
+    # end to end: tokens from pinned host memory in, outputs back, every step
+    xh = x0.cpu().pin_memory(); yh = torch.empty_like(xh).pin_memory(); xd = torch.empty_like(x0)
+    n_e2e = max(1, min(a.steps, 10))
+    torch.cuda.synchronize(); dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        xd.copy_(xh, non_blocking=True)
+        out, _ = step(xd)
+        yh.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    dist.barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+    # parity of the sharded layer against the single-GPU entry point on rank 0's tokens
+    y_ep, sel_ep, _ = layers[0].forward(x0)
+    par = None
+    if rank == 0:
+        full = [P.ep_gpu.expert_weights(50, 0, e, H, I, dev) for e in range(E + 1)]
+        ref_layer = P.MoeLayer(layers[0].router, layers[0].bias, full[:E], full[E], topk, H, I)
+        y_ref, sel_ref, _ = P.moe_forward(ref_layer, x0)
+        par = {'rel_l2': ((y_ep - y_ref).norm() / y_ref.norm()).item(), 'sel_equal': bool(torch.equal(sel_ep, sel_ref))}
+    stats = [L.ep.last_stats for L in layers]
+    if rank != 0:
+        return
+    total_b = b.item()
+    val = total_b / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        'metric': 'nvfp4_moe_ep_hbm_tbps', 'value': val, 'unit': 'TB/s', 'n_gpus': world, 'steps': a.steps, 'warmup': a.warmup,
+        'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
+        'dtype': 'nvfp4 weights, f16 products, f32 accumulate', 'data': 'synthetic',
+        'config': {'workload': 'expert-parallel MoE: %d tokens x 4096, 144 experts (%d per GPU), top-8 + shared expert, Zipf(1.1) routing bias, 3 stacked layers (configs[4])' % (T, E // world),
+                   'l2': 'inputs larger than L2: %.1f GB of expert weights per rank' % (Lyr * (E // world + 1) * layers[0].expert_bytes / 1e9),
+                   'collective': 'NCCL all_to_all_single: counts, token rows (fp32), expert ids; reverse for outputs'},
+        'tokens_per_s': T / (ms * 1e-3), 'us_per_layer': ms * 1e3 / Lyr,
+        'roofline': {'bound': 'hbm', 'kernel': 'k_expert_act', 'achieved': val * 1e3 / world, 'peak': peak, 'unit': 'GB/s per GPU',
+                     'frac': val * 1e3 / world / peak, 'traffic': None},
+        'e2e': {'value': total_b / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
+                'h2d_bytes_per_step': Tl * H * 4 * world, 'd2h_bytes_per_step': Tl * H * 4 * world},
+        'gpu_launches': a.steps * Lyr * 6, 'clocks': cs.summary(), 'ep_parity_vs_single_gpu': par, 'rank0_layer_stats': stats,
+        'cpu_baseline': None,
+    }))
+
+
 # ---- CPU baseline: the reference's CPU path restated (torch dequantise, then matmul) ------------
 
 def cpu_siblings_step(host_sets, x):
@@ -279,6 +368,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=50)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--quick', action='store_true', help='headline only, no sub-workloads')
+    ap.add_argument('--ep-tokens', type=int, default=256, help='tokens per step of the expert-parallel workload (N > 1)')
     ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,siblings,moe,quant)')
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
@@ -300,7 +390,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group('nccl', device_id=torch.device('cuda', local))
         dist.barrier()
-        raise SystemExit('expert-parallel MoE bench is not wired yet')
+        bench_ep(P, a, rank, local, world, peak)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     copies = 10                                        # 10 x 29.7 MB = 297 MB per rotation, > 2x L2
     ms, nbytes, clocks, state = bench_siblings(P, 1, a.steps, a.warmup, copies, sampler_index=local)
