@@ -37,5 +37,7 @@ int nvfp4_math_mode();
 // gemv_tma.cu: single-row (M = 1) bulk-copy pipelined kernel; returns B200_ENOTIMPL when the
 // shapes / alignments it needs do not hold, and the caller then uses the general kernel.
 int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
+// gemv_umma.cu: single-row tensor-core (tcgen05 block-scaled) kernel; same contract.
+int nvfp4_multi_umma(const GemvParams& p, cudaStream_t s);
 
 }  // namespace b200

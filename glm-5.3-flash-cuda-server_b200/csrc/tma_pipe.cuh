@@ -11,6 +11,7 @@
 namespace b200 {
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;          // polls; each poll may block for a HW time slice
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;   // and never longer than about a second
 
 // A kernel receives `status`, the address of the library's device status word: 0 = no wait has
 // ever given up; otherwise (code << 16 | blockIdx.x & 0xffff) of the first one that did.
@@ -37,9 +38,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false (after recording `code`) if the barrier did not flip within the limit.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned* status, unsigned code) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && global_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
     atomicCAS(status, 0u, (code << 16) | (blockIdx.x & 0xffffu));
     return false;
 }
