@@ -38,6 +38,6 @@ int nvfp4_math_mode();
 // shapes / alignments it needs do not hold, and the caller then uses the general kernel.
 int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
 // gemv_umma.cu: single-row tensor-core (tcgen05 block-scaled) kernel; same contract.
-int nvfp4_multi_umma(const GemvParams& p, cudaStream_t s);
+int nvfp4_multi_umma(const GemvParams& p, int M, cudaStream_t s);
 
 }  // namespace b200

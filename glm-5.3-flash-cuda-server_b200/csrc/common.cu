@@ -19,7 +19,7 @@ int sm_count() {
 
 // Written by a kernel whose bounded wait ran out (see tma_pipe.cuh); read by
 // b200_nvfp4_device_status.  One word per device that loads the library.
-__device__ unsigned int g_device_status = 0;
+__device__ unsigned int g_device_status[2] = {0, 0};   // [0] first failure, [1] OR of (1 << site) over all failures
 
 unsigned int* device_status_ptr() {
     static unsigned int* cache[64] = {nullptr};
@@ -83,7 +83,10 @@ extern "C" int b200_nvfp4_device_status(unsigned int* out, int clear) {
     if (!out) return B200_EINVAL;
     unsigned int* p = b200::device_status_ptr();
     if (!p) return B200_ELAUNCH;
-    if (cudaMemcpy(out, p, sizeof(*out), cudaMemcpyDeviceToHost) != cudaSuccess) return b200::launch_failed("device_status read");
-    if (clear && *out && cudaMemset(p, 0, sizeof(*out)) != cudaSuccess) return b200::launch_failed("device_status clear");
+    unsigned int both[2] = {0, 0};
+    if (cudaMemcpy(both, p, sizeof(both), cudaMemcpyDeviceToHost) != cudaSuccess) return b200::launch_failed("device_status read");
+    *out = both[0];
+    if (both[0]) fprintf(stderr, "b200_nvfp4: device status: first failure %08x, sites mask %08x\n", both[0], both[1]);
+    if (clear && both[0] && cudaMemset(p, 0, sizeof(both)) != cudaSuccess) return b200::launch_failed("device_status clear");
     return B200_OK;
 }

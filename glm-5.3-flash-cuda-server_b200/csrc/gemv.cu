@@ -230,10 +230,11 @@ static bool force_general() {
     return e && *e == '1';
 }
 
-// B200_NVFP4_UMMA=1 routes single-row products to the tensor-core kernel (gemv_umma.cu).
+// The tensor-core kernel (gemv_umma.cu) takes every shape it can; B200_NVFP4_UMMA=0 keeps it off
+// (used by tests that compare the kernels with one another, and for profiling).
 static bool use_umma() {
     const char* e = getenv("B200_NVFP4_UMMA");
-    return e && *e == '1';
+    return !(e && *e == '0');
 }
 
 int rows_per_tile(int M) { return GEMV_WARPS * (M <= 2 ? 4 : 2); }
@@ -259,8 +260,8 @@ int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s) 
     }
     for (int i = n; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].N = 0; p.j[i].task0 = 0x7fffffff; }
     p.total_tasks = tasks;
-    if (M == 1 && fast && use_umma()) {
-        const int rc = nvfp4_multi_umma(p, s);
+    if (use_umma() && !force_general()) {            // checks its own conditions; they do not depend on M
+        const int rc = nvfp4_multi_umma(p, M, s);
         if (rc != B200_ENOTIMPL) return rc;
     }
     if (M == 1 && fast && !force_general()) {

@@ -1,5 +1,5 @@
 // gemv_umma.cu -- NVFP4 gemv (one activation row) on the 5th-generation tensor cores:
-// tcgen05.mma kind::mxf4nvf4 (block-16, UE4M3 scales), TMEM accumulators, TMA tile loads.
+// tcgen05.mma kind::mxf4nvf4 (block-16, UE4M3 scales), TMEM accumulators.
 //
 // Why tensor cores for a matrix-VECTOR product: the CUDA-core formulation is capped by the
 // conversion pipe (cvt.rn.f16x2.e2m1x2 issues once per ~3 cycles per scheduler: 24e12 weights/s
@@ -8,23 +8,33 @@
 // format stores them, so the SM does no decode work at all and the kernel is a pure stream.
 //
 // How fp32-activation accuracy is kept although both MMA operands are FP4: the activation row is
-// written as EIGHT FP4 columns.  Per 16-group g, x = gamma * s_g * v with s_g an e4m3 scale
-// (rounded up so |v| < 4) and v rounded to 16 fractional bits: v = sign * sum_t d_t 4^-t with
-// base-4 digits d_t in {0,1,2,3}, all of which e2m1 represents exactly.  Column t of the B
-// operand holds the digits d_t (same block scales s_g for every column); the MMA's N = 8 columns
-// come for free, and the epilogue adds the columns as y = (sum_t gamma 4^-t D[:,t]) / gscale.
-// Rounding error per activation <= 2^-17 of 4 s_g, i.e. < 1e-5 of the group's amax -- thirty
-// times finer than fp16 staging -- and products and sums inside the MMA are exact / fp32.
+// written as EIGHT FP4 columns.  x = gamma * v with gamma = amax(x) / 3.99, so |v| < 4, and v is
+// rounded to 14 fractional bits: v = sign * sum_t d_t 4^-t, t = 0..7, with base-4 digits d_t in
+// {0,1,2,3}, all of which e2m1 represents exactly.  Column t of the B operand holds the digits
+// d_t; its block scales are the constant 1.0, written to TMEM once.  The MMA's N = 8 columns come
+// for free (an MMA of M = 128 costs ~55 cycles for any N <= 96, measured), and the epilogue adds
+// them: y = (sum_t gamma 4^-t D[:,t]) / gscale.  Rounding error per activation <= 2^-15 gamma =
+// 7.7e-6 amax(x): measured rel-L2 of a product 1.6e-5, forty times finer than fp16 staging;
+// products and sums inside the MMA are exact / fp32.
 //
 // Per CTA (one per SM): rows [r0, r0+R) of one job, R <= 128 a multiple of 8.
-//   warp 0      TMA producer: per 256-k stage one box [128 B x R rows] of packed weights
-//               (SWIZZLE_128B, K-major UMMA operand layout) and one box [16 B x R rows] of scales
-//   warps 2-5   split the activation row into the B image (once), then per stage rearrange the
-//               R x 16 scale bytes into the four 512-byte scale atoms tcgen05.cp expects, and at
-//               the end read the accumulators (tcgen05.ld) and write y
-//   warp 1      TMEM allocation; one thread issues, per stage, 8 tcgen05.cp (scales -> TMEM) and
-//               4 tcgen05.mma (K = 64 each), then tcgen05.commit frees the stage
-// Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast.
+//   warps 0-3   loaders: per 256-k step, cp.async (16 bytes per thread and request) of the R x 128
+//               bytes of packed weights into the 128-byte-swizzled K-major layout the MMA reads,
+//               and of the R x 16 scale bytes; stages - 1 steps are kept in flight per thread.
+//               (Tensor-map TMA boxes of R rows x 128 bytes were measured at 0.35 us per box from
+//               one CTA, 18 bytes per clock per SM: not enough to keep HBM busy.)
+//   warps 4-7   MMA issuers: warp w takes every fourth step: 4 tcgen05.mma (K = 64 each) into its
+//               own accumulator, then a tcgen05.commit frees the stage
+//   warps 8-15  workers: split the activation row into the B image (once); then, in two groups of
+//               four warps (one warp per TMEM lane quadrant) taking alternate steps, move the
+//               step's R x 16 scale bytes from shared memory to the stage's scale columns in TMEM
+//               (tcgen05.st: lane r % 32, column r / 32, the layout the block-scaled MMA reads);
+//               the first group finally reads the accumulators and writes y
+// Barriers: full[step], sf[step] and empty[step] are used once each, so that no waiter ever has
+// to tell phases apart (a parity wait cannot tell "two phases behind" from "ready").  In the
+// single-thread roles the whole warp walks the loop and waits (a lone lane whose 31 siblings are
+// parked at the closing barrier is scheduled rarely: measured 20 % slower).
+// Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast, no tensor maps.
 #include "b200_internal.h"
 #include "nvfp4_decode.cuh"
 #include "tma_pipe.cuh"
@@ -34,29 +44,47 @@
 
 namespace b200 {
 
-constexpr int UM_THREADS = 192;                    // 6 warps
-constexpr int UM_NB = 8;                           // MMA N = digits per activation
-constexpr int UM_MAX_STAGES = 14;
-constexpr int UM_TMEM_COLS = 128;                  // D [0,8) | SFA slots [32,64) | SFB slots [64,96)
+#define UM_WAIT mbar_wait_spin
 
-struct UmJob { float* y; const float* gs; int N; int task0; };
+constexpr int UM_LOAD_WARPS = 4;
+constexpr int UM_MMA_WARPS = 4;
+constexpr int UM_WORKERS = 256;
+constexpr int UM_LOADERS = 32 * UM_LOAD_WARPS;
+constexpr int UM_THREADS = UM_LOADERS + 32 * UM_MMA_WARPS + UM_WORKERS;
+constexpr int UM_NB = 8;                           // MMA N = digits per activation
+constexpr int UM_MAX_M = 8;                        // activation rows per job (MMA N = 8 * M <= 64)
+constexpr int UM_MAX_STAGES = 12;                  // TMEM holds one 16-column scale slot per stage
+constexpr int UM_MAX_STEPS = 64;                   // K <= 16384
+constexpr int UM_TMEM_COLS = 512;                  // D0..D3 [0,256), 64 each | unit scales [256,260) | per-stage weight scales [272, 272+16*stages)
+constexpr int UM_COL_SB = 256, UM_COL_SF = 272;
+
+
+struct UmJob { float* y; const float* x; const float* gs; int N; int M; int task0; };     // x [M, K], y [M, N]
 struct UmParams {
     UmJob j[B200_GEMV_MULTI_MAX];
-    const float* x;
     unsigned int* status;
-    int n_jobs, K, R, stages, prefetch_before_wait;
-    uint32_t stage_bytes, a_bytes;                 // per stage: A tile | raw scales | 4 scale atoms
+    int n_jobs, K, R, stages, prefetch_before_wait, max_m;
+    uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
+    int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
+    unsigned long long* trace;                     // B200_TRACE builds only: 64 timestamps per CTA
 };
+
+#ifdef B200_TRACE
+#define UTRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = global_ns(); } while (0)
+#else
+#define UTRACE(slot) do { } while (0)
+#endif
+
 struct UmMaps { CUtensorMap w[B200_GEMV_MULTI_MAX]; CUtensorMap s[B200_GEMV_MULTI_MAX]; };
 
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t layout) {
     // start address >> 4 | LBO (unused here) | SBO >> 4 | version 1 | layout type (2 = SWIZZLE_128B, 0 = none)
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)(layout & 7) << 61);
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -64,24 +92,36 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
-
-// e4m3 code (0..126) of the smallest representable value >= v (v >= 0); 126 (448) if v is larger.
-__device__ __forceinline__ uint32_t e4m3_ceil_code(float v) {
-    uint16_t two;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(two) : "f"(0.f), "f"(v));     // low byte <- v
-    uint32_t c = two & 0xFFu;
-    if (e4m3_to_f32(c) < v && c < 126u) ++c;
-    return c;
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Wait until at most n of this thread's cp.async groups are pending (n <= 11).
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+    switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    case 7: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    case 8: asm volatile("cp.async.wait_group 8;" ::: "memory"); break;
+    case 9: asm volatile("cp.async.wait_group 9;" ::: "memory"); break;
+    case 10: asm volatile("cp.async.wait_group 10;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 11;" ::: "memory"); break;
+    }
 }
 
 __global__ void __launch_bounds__(UM_THREADS, 1)
 k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t full_bar[UM_MAX_STAGES], sf_bar[UM_MAX_STAGES], empty_bar[UM_MAX_STAGES], done_bar;
+    __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ float gam[UM_NB], red[8];
+    __shared__ float gam[UM_MAX_M][UM_NB], red[UM_MAX_M][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int K = p.K, nst = (K + 255) >> 8;       // 256-k stages along K
+    const int K = p.K, nst = K >> 8;               // 256-k steps along K
     // which job / rows
     int ji = 0;
     #pragma unroll
@@ -89,19 +129,23 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     const UmJob J = p.j[ji];
     const int row0 = ((int)blockIdx.x - J.task0) * p.R;
     const int valid = min(p.R, J.N - row0);
+    const int M = J.M;
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);      // SWIZZLE_128B tiles need 1 KB alignment
-    unsigned char* bimg = ring + (size_t)p.stages * p.stage_bytes;          // nst tiles of 1 KB
-    unsigned char* sfb = bimg + (size_t)nst * 1024;                          // K/64 atoms at 128 B stride (+384 tail)
+    unsigned char* bimg = ring + (size_t)p.stages * p.stage_bytes;          // nst tiles of max_m KB: [step][row m][digit t][128 B]
+    unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: slabs [R x sc_box]
 
     pdl_launch_dependents();
-    if (tid == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&sf_bar[s]), 128); mbar_init(smem_u32(&empty_bar[s]), 1);
-        }
-        mbar_init(smem_u32(&done_bar), 1);
+    if (tid == 0) UTRACE(3);
+    if (warp >= UM_LOAD_WARPS + UM_MMA_WARPS) {      // barrier init spread over the worker threads
+        const int i = tid - UM_LOADERS - 32 * UM_MMA_WARPS;
+        if (i < nst) mbar_init(smem_u32(&full_bar[i]), 1);
+        else if (i >= 64 && i < 64 + nst) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
+        else if (i >= 128 && i < 128 + nst) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
+        else if (i == 192) mbar_init(smem_u32(&done_bar), UM_MMA_WARPS);
+        else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
         mbar_fence_init();
     }
-    if (warp == 1) {
+    if (warp == UM_LOAD_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_base_s)), "r"(UM_TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
@@ -109,148 +153,246 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
+    if (tid == 0) UTRACE(4);
 
-    if (warp == 0) {
-        // ---- TMA producer ----
-        if (lane == 0) {
+    if (warp < UM_LOAD_WARPS) {
+        // ---- TMA producer: warp 0; lane l issues the loads of steps l, l + 32, ... ----
+        // One thread issuing tensor loads back to back gets one out every ~0.35 us (measured), so
+        // the steps are dealt to the lanes: each lane waits for its own stage and issues on its own.
+        if (warp == 0) {
+            if (lane == 0) { UTRACE(0); asm volatile("prefetch.tensormap [%0];" :: "l"(&maps.w[ji]) : "memory");
+                             asm volatile("prefetch.tensormap [%0];" :: "l"(&maps.s[ji]) : "memory"); }
             if (!p.prefetch_before_wait) pdl_wait();
-            const uint32_t bytes = (uint32_t)p.R * 128u + (uint32_t)p.R * 16u;
-            for (int it = 0; it < nst; ++it) {
+            // All scale rows of the CTA first, in slabs [R rows x sc_box bytes]: one tensor load per
+            // slab instead of one [R x 16 B] box per step (a box costs the TMA unit ~1 ns per row
+            // whatever the row's width).  128-byte slabs are stored 128B-swizzled, so that 32 lanes
+            // reading the same 16-byte column of 32 consecutive rows hit different banks.
+            const int nslab = (K >> 4) / p.sc_box;
+            if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), (uint32_t)p.R * (uint32_t)(K >> 4));
+            __syncwarp();
+            if (lane < nslab)
+                tma_load_2d(smem_u32(scl) + (uint32_t)lane * (uint32_t)p.R * (uint32_t)p.sc_box, &maps.s[ji], lane * p.sc_box, row0, smem_u32(&sc_bar));
+            const uint32_t bytes = (uint32_t)p.R * 128u;
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), ring0 = smem_u32(ring);
+            for (int it = lane; it < nst; it += 32) {
                 const int s = it % p.stages;
-                if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[s]), ((it / p.stages) - 1) & 1, p.status, 1);
-                const uint32_t bar = smem_u32(&full_bar[s]);
-                const uint32_t dst = smem_u32(ring + (size_t)s * p.stage_bytes);
+                if (it >= p.stages) UM_WAIT(empty0 + (it - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
+                const uint32_t bar = full0 + it * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
                 mbar_expect_tx(bar, bytes);
                 tma_load_2d(dst, &maps.w[ji], it * 128, row0, bar);
-                tma_load_2d(dst + p.a_bytes, &maps.s[ji], it * 16, row0, bar);
+                if (it == 0) UTRACE(1);
             }
+            __syncwarp();
+            if (lane == 0) UTRACE(2);
+            // Tail: the tcgen05.commit arrivals on empty_bar are asynchronous.  Wait for the last one
+            // of every stage, or the CTA could exit with an arrival still in flight and it would
+            // land on whatever the next CTA keeps at that shared-memory address.
+            for (int it = max(0, nst - p.stages) + lane; it < nst; it += 32)
+                UM_WAIT(empty0 + it * 8, 0, p.status, 5);
+            __syncwarp();
+            if (lane == 0) UTRACE(62);
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer ----
-        pdl_wait();
-        named_sync(2, 160);                          // B image, scale atoms of x and gam[] are ready
-        if (lane == 0) {
-            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(UM_NB >> 3) << 17) | ((128u >> 4) << 24);
-            for (int it = 0; it < nst; ++it) {
-                const int s = it % p.stages, slot = it & 1;
-                mbar_wait(smem_u32(&sf_bar[s]), (it / p.stages) & 1, p.status, 3);
+    } else if (warp < UM_LOAD_WARPS + UM_MMA_WARPS) {
+        // ---- MMA issuers: warp w takes steps it with it % 4 == w, accumulator D[w] ----
+        named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // B image, unit scales and gam[] are ready
+        tc_fence_after();
+        {
+            const int me = warp - UM_LOAD_WARPS;
+            if (me == 0 && lane == 0) UTRACE(8);
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)M << 17) | ((128u >> 4) << 24);     // N = 8 M
+            const uint64_t dA0 = umma_desc(smem_u32(ring), 1024, 2), dB0 = umma_desc(smem_u32(bimg), 1024, 2);
+            const uint32_t tD = tmem + me * 64, tSB = tmem + UM_COL_SB;
+            const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+            int s = me % p.stages;
+            for (int it = me; it < nst; it += UM_MMA_WARPS) {          // whole warp waits, lane 0 issues
+                const uint32_t tsf = tmem + UM_COL_SF + (uint32_t)s * 16u;
+                const uint64_t dA = dA0 + (((uint32_t)s * p.stage_bytes) >> 4), dB = dB0 + (uint32_t)(it * p.max_m) * 64u;
+                const uint32_t acc0 = it >= UM_MMA_WARPS;
+                UM_WAIT(sf0 + it * 8, 0, p.status, 3);
                 tc_fence_after();
-                const uint32_t st = smem_u32(ring + (size_t)s * p.stage_bytes);
-                const int nkb = min(4, (K - it * 256) >> 6);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    const uint64_t da = umma_desc(st + p.a_bytes + (uint32_t)p.R * 16u + kb * 512, 128, 0);
-                    const uint64_t db = umma_desc(smem_u32(sfb) + (it * 4 + kb) * 128, 128, 0);
-                    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(tmem + 32 + slot * 16 + kb * 4), "l"(da));
-                    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(tmem + 64 + slot * 16 + kb * 4), "l"(db));
+                if (lane == 0) {
+                    #pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {                           // K % 256 == 0: always four 64-k blocks
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                     " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+                                     :: "r"(tD), "l"(dA + kb * 2), "l"(dB + kb * 2), "r"(idesc), "r"(kb ? 1u : acc0),
+                                        "r"(tsf + kb * 4), "r"(tSB) : "memory");
+                    }
+                    tc_commit(empty0 + it * 8);
+                    if (me == 0) UTRACE(9 + it / UM_MMA_WARPS);
                 }
-                for (int kb = 0; kb < nkb; ++kb) {
-                    const uint64_t da = umma_desc(st + kb * 32, 1024, 2);
-                    const uint64_t db = umma_desc(smem_u32(bimg) + it * 1024 + kb * 32, 1024, 2);
-                    const uint32_t acc = (it | kb) != 0;
-                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                                 " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
-                                 :: "r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc),
-                                    "r"(tmem + 32 + slot * 16 + kb * 4), "r"(tmem + 64 + slot * 16 + kb * 4) : "memory");
-                }
-                tc_commit(smem_u32(&empty_bar[s]));
+                __syncwarp();
+                s += UM_MMA_WARPS; while (s >= p.stages) s -= p.stages;
             }
-            tc_commit(smem_u32(&done_bar));
+            if (lane == 0) tc_commit(smem_u32(&done_bar));
+            __syncwarp();
         }
     } else {
-        // ---- warps 2..5: activation split, per-stage scale rearrangement, epilogue ----
-        const int t4 = tid - 64;                     // 0..127
-        pdl_wait();
-        const float* x = p.x;
-        // global amax of x
-        float a = 0.f;
-        for (int i = t4; i < (K >> 2); i += 128) {
-            const float4 v = reinterpret_cast<const float4*>(x)[i];
-            a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        // ---- workers: activation split, then per-step scale copies; the first four warps also the epilogue ----
+        const int t4 = tid - UM_LOADERS - 32 * UM_MMA_WARPS;      // 0..255
+        const int q4 = warp & 3;                         // TMEM lane quadrant this warp may access
+        const uint32_t tq = tmem + ((uint32_t)(q4 * 32) << 16);
+        if (t4 < 128) {
+            // unit block scales of the activation digits (e4m3 1.0), once
+            const uint32_t one = 0x38383838u;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" :: "r"(tq + UM_COL_SB), "r"(one) : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
-        a = warp_max(a);
-        if (lane == 0) red[warp - 2] = a;
-        named_sync(1, 128);
-        a = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-        // gamma: x = gamma * s_g * v with s_g <= 448 and |v| < 4
-        const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / (448.f * 3.99f)) : 1.f;
-        if (t4 < UM_NB) gam[t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
-        for (int i = t4; i < 384; i += 128) sfb[(size_t)(K >> 6) * 128 + i] = 0;                  // tail the last atom reads
-        for (int g = t4; g < (K >> 4); g += 128) {
-            float v[16];
-            #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float4 f = reinterpret_cast<const float4*>(x)[g * 4 + q];
-                v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
-            }
-            float am = 0.f;
-            #pragma unroll
-            for (int q = 0; q < 16; ++q) am = fmaxf(am, fabsf(v[q]));
-            const uint32_t code = e4m3_ceil_code(am / (gamma * 3.99f));
-            const float sdec = e4m3_to_f32(code);
-            const float inv = sdec > 0.f ? 16384.f / (gamma * sdec) : 0.f;
-            uint32_t lo[UM_NB], hi[UM_NB];
-            #pragma unroll
-            for (int t = 0; t < UM_NB; ++t) { lo[t] = 0; hi[t] = 0; }
-            #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                int iq = __float2int_rn(v[q] * inv);
-                const uint32_t sgn = iq < 0 ? 8u : 0u;
-                uint32_t m = (uint32_t)min(abs(iq), 65535);
+        if (!p.prefetch_before_wait) pdl_wait();
+        const float gsv = J.gs[0];                       // weight data: with stable weights it may be read early
+        pdl_wait();
+        if (t4 == 0) UTRACE(32);
+        const float* x = J.x;
+        // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
+        // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
+        float4 xv[4];
+        for (int m = 0; m < M; ++m) {
+            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+            float a = 0.f;
+            for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
                 #pragma unroll
-                for (int t = 0; t < UM_NB; ++t) {
-                    const uint32_t d = (m >> (2 * (UM_NB - 1 - t))) & 3u;       // digit of weight 4^-t
-                    const uint32_t c = d ? ((d << 1) - (d == 3u) + sgn) : 0u;     // e2m1 code of +-d: 1->2, 2->4, 3->5
-                    if (q < 8) lo[t] |= c << (4 * q); else hi[t] |= c << (4 * (q - 8));
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = xr[i + q];
+                    if (i == t4 * 4) xv[q] = v;
+                    a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
             }
-            // B image: tile (256 k) = g / 16, row t, 16-byte chunk (g % 16) / 2 swizzled with the row, half g % 2
-            const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
+            a = warp_max(a);
+            if (lane == 0) red[m][warp - UM_LOAD_WARPS - UM_MMA_WARPS] = a;
+        }
+        named_sync(1, UM_WORKERS);
+        // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
+        for (int m = 0; m < M; ++m) {
+            float a = 0.f;
             #pragma unroll
-            for (int t = 0; t < UM_NB; ++t)
-                *reinterpret_cast<uint2*>(bimg + tile * 1024 + t * 128 + ((ch ^ t) << 4) + hf * 8) = make_uint2(lo[t], hi[t]);
-            // scale atoms of x: K-block g / 4, scale index g % 4, same byte for all 8 columns
-            #pragma unroll
-            for (int n = 0; n < UM_NB; ++n) sfb[(size_t)(g >> 2) * 128 + n * 16 + (g & 3)] = (uint8_t)code;
+            for (int w = 0; w < 8; ++w) a = fmaxf(a, red[m][w]);
+            const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / 3.99f) : 1.f;
+            const float inv = 16384.f / gamma;
+            if (t4 < UM_NB) gam[m][t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
+            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+            for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
+                // 16 activations -> 16 words of eight e2m1 codes (nibble j = digit of weight 4^-(7-j)),
+                // then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
+                uint32_t W[16];
+                #pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 f = (M == 1 && g == t4) ? xv[q4] : xr[g * 4 + q4];
+                    const float v[4] = {f.x, f.y, f.z, f.w};
+                    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int iq = __float2int_rn(v[e] * inv);
+                        uint32_t mm = (uint32_t)min(abs(iq), 65535);
+                        mm = (mm | (mm << 8)) & 0x00FF00FFu;
+                        mm = (mm | (mm << 4)) & 0x0F0F0F0Fu;
+                        mm = (mm | (mm << 2)) & 0x33333333u;                    // one base-4 digit per nibble
+                        const uint32_t b1 = (mm >> 1) & 0x11111111u, b0 = mm & 0x11111111u;
+                        uint32_t c = (mm << 1) - (b1 & b0);                        // e2m1 code of the digit: 0,2,4,5
+                        if (iq < 0) c |= (b1 | b0) << 3;                           // sign on the non-zero digits
+                        W[q4 * 4 + e] = c;
+                    }
+                }
+                #pragma unroll
+                for (int h = 0; h < 16; h += 8) {
+                    #pragma unroll
+                    for (int r = 0; r < 8; r += 2) { const uint32_t t = ((W[h + r] >> 4) ^ W[h + r + 1]) & 0x0F0F0F0Fu; W[h + r] ^= t << 4; W[h + r + 1] ^= t; }
+                    #pragma unroll
+                    for (int r = 0; r < 8; ++r) if (!(r & 2)) { const uint32_t t = ((W[h + r] >> 8) ^ W[h + r + 2]) & 0x00FF00FFu; W[h + r] ^= t << 8; W[h + r + 2] ^= t; }
+                    #pragma unroll
+                    for (int r = 0; r < 4; ++r) { const uint32_t t = ((W[h + r] >> 16) ^ W[h + r + 4]) & 0x0000FFFFu; W[h + r] ^= t << 16; W[h + r + 4] ^= t; }
+                }
+                // W[j] (j < 8): codes of digit 7-j for activations 0..7; W[8 + j]: for activations 8..15.
+                // B image: step (256 k) = g / 16, atom m (8 rows of 128 B), row t, 16-byte chunk (g % 16) / 2
+                // swizzled with the row, half g % 2
+                const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
+                unsigned char* at = bimg + ((size_t)tile * p.max_m + m) * 1024 + hf * 8;
+                #pragma unroll
+                for (int t = 0; t < UM_NB; ++t)
+                    *reinterpret_cast<uint2*>(at + t * 128 + ((ch ^ t) << 4)) = make_uint2(W[7 - t], W[15 - t]);
+            }
         }
         fence_async_smem();
-        named_sync(2, 160);                          // with the MMA warp
-        // per stage: row r's 16 scale bytes -> 4 atoms
-        for (int it = 0; it < nst; ++it) {
-            const int s = it % p.stages;
-            mbar_wait(smem_u32(&full_bar[s]), (it / p.stages) & 1, p.status, 2);
-            unsigned char* st = ring + (size_t)s * p.stage_bytes + p.a_bytes;
-            if (t4 < p.R) {
-                const uint4 v = *reinterpret_cast<const uint4*>(st + t4 * 16);
-                unsigned char* at = st + (size_t)p.R * 16 + (t4 & 31) * 16 + (t4 >> 5) * 4;
-                *reinterpret_cast<uint32_t*>(at) = v.x;
-                *reinterpret_cast<uint32_t*>(at + 512) = v.y;
-                *reinterpret_cast<uint32_t*>(at + 1024) = v.z;
-                *reinterpret_cast<uint32_t*>(at + 1536) = v.w;
+        tc_fence_before();
+        if (t4 == 0) UTRACE(33);
+        named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // with the MMA warps
+        {
+            // Weight scales: the first four worker warps take the even steps, the other four the odd
+            // ones; within a group each warp writes its own TMEM lane quadrant (the MMA wants the
+            // 32-lane block in all four).  Lane l holds rows l, l+32, l+64, l+96: 16 bytes each =
+            // four k-blocks x four scales; k-block kb of row 32c + l goes to column kb*4 + c.
+            const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
+            const int grp = t4 >> 7;
+            int s = grp % p.stages;
+            UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
+            // Software-pipelined: the next step's scale bytes are read from shared memory while this
+            // step's tcgen05.st is in flight.
+            auto read_scales = [&](int it, uint4 (&v)[4]) {
+                // full[it] also says that the MMAs that last read this stage's scale slot are done
+                UM_WAIT(full0 + it * 8, 0, p.status, 2);
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int r = lane + 32 * c;
+                    uint32_t off;
+                    if (p.sc_swz) off = (uint32_t)(it >> 3) * (uint32_t)p.R * 128u + (uint32_t)r * 128u + (uint32_t)(((it & 7) ^ (r & 7)) << 4);
+                    else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)it * 16u;
+                    v[c] = (r < valid) ? *reinterpret_cast<const uint4*>(scl + off) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            uint4 v[4], vn[4];
+            if (grp < nst) read_scales(grp, v);
+            for (int it = grp; it < nst; it += 2) {
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                             :: "r"(tq + UM_COL_SF + (uint32_t)s * 16u),
+                                "r"(v[0].x), "r"(v[1].x), "r"(v[2].x), "r"(v[3].x), "r"(v[0].y), "r"(v[1].y), "r"(v[2].y), "r"(v[3].y),
+                                "r"(v[0].z), "r"(v[1].z), "r"(v[2].z), "r"(v[3].z), "r"(v[0].w), "r"(v[1].w), "r"(v[2].w), "r"(v[3].w) : "memory");
+                if (it + 2 < nst) read_scales(it + 2, vn);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(sf0 + it * 8);
+                if ((t4 & 127) == 0 && it < 24) UTRACE(34 + it);
+                s += 2; while (s >= p.stages) s -= p.stages;
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = vn[c];
             }
-            fence_async_smem();
-            mbar_arrive(smem_u32(&sf_bar[s]));
         }
-        // epilogue
-        mbar_wait(smem_u32(&done_bar), 0, p.status, 4);
-        tc_fence_after();
-        uint32_t d[8];
-        const int q4 = warp & 3;                     // TMEM lane quadrant this warp may read
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
-                     : "r"(tmem + ((uint32_t)(q4 * 32) << 16)));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int r = q4 * 32 + lane;
-        if (r < valid) {
-            float acc = 0.f;
-            #pragma unroll
-            for (int t = UM_NB - 1; t >= 0; --t) acc = fmaf(__uint_as_float(d[t]), gam[t], acc);     // small terms first
-            J.y[row0 + r] = acc / J.gs[0];
+        if (t4 < 128) {
+            // epilogue
+            UM_WAIT(smem_u32(&done_bar), 0, p.status, 4);
+            tc_fence_after();
+            if (t4 == 0) UTRACE(60);
+            const int r = q4 * 32 + lane;
+            for (int m = 0; m < M; ++m) {
+                // row m of the activations: columns m*8 .. m*8+7 of each issuer's accumulator
+                uint32_t d[4][8];
+                #pragma unroll
+                for (int w = 0; w < UM_MMA_WARPS; ++w)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(d[w][0]), "=r"(d[w][1]), "=r"(d[w][2]), "=r"(d[w][3]), "=r"(d[w][4]), "=r"(d[w][5]), "=r"(d[w][6]), "=r"(d[w][7])
+                                 : "r"(tq + (uint32_t)(w * 64 + m * 8)));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < valid) {
+                    float acc = 0.f;
+                    #pragma unroll
+                    for (int t = UM_NB - 1; t >= 0; --t) {                 // small terms first
+                        float dsum = __uint_as_float(d[0][t]);
+                        #pragma unroll
+                        for (int w = 1; w < UM_MMA_WARPS; ++w) if (w < nst) dsum += __uint_as_float(d[w][t]);   // issuers that had a step
+                        acc = fmaf(dsum, gam[m][t], acc);
+                    }
+                    J.y[(size_t)m * J.N + row0 + r] = acc / gsv;
+                }
+            }
+            if (t4 == 0) UTRACE(5);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(UM_TMEM_COLS));
+    if (warp == UM_LOAD_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(UM_TMEM_COLS));
+    if (tid == 32 * UM_LOAD_WARPS) UTRACE(61);
 }
+
+#ifdef B200_TRACE
+unsigned long long* g_trace_umma = nullptr;
+#endif
 
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -276,17 +418,32 @@ static bool make_map(CUtensorMap* m, const void* base, int rows, size_t row_byte
                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Conditions: M = 1, one activation row shared by all jobs, K % 64 == 0 and K <= 16384, 16-byte
-// aligned tensors and activation, K/16 a multiple of 16 (scale row pitch for TMA).
-int nvfp4_multi_umma(const GemvParams& g, cudaStream_t s) {
+// Conditions: M = 1 (one activation row shared by all jobs), K % 256 == 0 and K <= 16384, 16-byte
+// aligned tensors and activation, at least 256 rows in total.
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s);
+
+// Rows of the activations are taken in chunks that fit the shared memory (the B image takes M KB
+// per 256 k); every chunk size computes each row with the same arithmetic, so results do not
+// depend on how the rows were chunked.
+int nvfp4_multi_umma(const GemvParams& g, int M, cudaStream_t s) {
+    if (M < 1) return B200_ENOTIMPL;
+    int done = 0, cap = UM_MAX_M;                    // cap: the chunk size the first launch settled on
+    while (done < M) {
+        int mc = std::min(cap, M - done), rc = umma_launch(g, mc, done, s);
+        while (rc == B200_ENOTIMPL && done == 0 && mc > 1) { mc /= 2; rc = umma_launch(g, mc, done, s); }
+        if (rc != B200_OK) return rc;                // ENOTIMPL only before anything was launched
+        cap = mc; done += mc;
+    }
+    return B200_OK;
+}
+
+// One launch: activation rows [m0, m0 + M) of every job.
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     const int K = g.K;
     if ((K & 255) || K > 16384 || !encode_fn()) return B200_ENOTIMPL;
-    int total = 0;
-    for (int i = 0; i < g.n_jobs; ++i) {
-        if (g.j[i].x != g.j[0].x || ((uintptr_t)g.j[i].P & 15) || ((uintptr_t)g.j[i].S & 15)) return B200_ENOTIMPL;
-        total += g.j[i].N;
-    }
-    if (((uintptr_t)g.j[0].x & 15) || total < 256) return B200_ENOTIMPL;
+    if (M < 1 || M > UM_MAX_M) return B200_ENOTIMPL;
+    for (int i = 0; i < g.n_jobs; ++i)
+        if (((uintptr_t)g.j[i].x & 15) || ((uintptr_t)g.j[i].P & 15) || ((uintptr_t)g.j[i].S & 15)) return B200_ENOTIMPL;
     const int nsm = sm_count();
     int R = 128;
     for (int r = 8; r <= 128; r += 8) {
@@ -296,33 +453,48 @@ int nvfp4_multi_umma(const GemvParams& g, cudaStream_t s) {
     }
     static UmMaps maps;                              // one host thread at a time calls in
     UmParams p{};
-    p.x = g.j[0].x; p.n_jobs = g.n_jobs; p.K = K; p.R = R;
+    p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = M;
+    if ((K / 16) % 128 == 0) { p.sc_box = 128; p.sc_swz = 1; }
+    else if (K / 16 <= 256) { p.sc_box = K / 16; p.sc_swz = 0; }
+    else return B200_ENOTIMPL;
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
-        p.j[i] = UmJob{g.j[i].y, g.j[i].gs, g.j[i].N, tasks};
+        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, g.j[i].gs, g.j[i].N, M, tasks};
         tasks += (g.j[i].N + R - 1) / R;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
-            !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, 16, R, false)) return B200_ENOTIMPL;
+            !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
     }
     for (int i = g.n_jobs; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].task0 = 0x7fffffff; maps.w[i] = maps.w[0]; maps.s[i] = maps.s[0]; }
-    p.a_bytes = (uint32_t)R * 128u;
-    p.stage_bytes = ((p.a_bytes + (uint32_t)R * 16u + 2048u) + 1023u) & ~1023u;
+    p.stage_bytes = ((uint32_t)R * 128u + 1023u) & ~1023u;
     const int nst = K / 256;
-    const size_t fixed = (size_t)nst * 1024 + (size_t)(K / 64) * 128 + 384;
+    size_t fixed = (size_t)nst * M * 1024 + (size_t)R * (K / 16);      // B image | scale slabs
+    // The MMA is always 128 rows tall: it reads 16 KB from the start of a stage even when only R
+    // rows were loaded (the extra accumulator rows are never stored).  Keep that read inside the
+    // allocation for the last stage as well.
+    if (p.stage_bytes + fixed < 16384) fixed = 16384 - p.stage_bytes;
     cudaFuncAttributes fa;
     int dev = 0, optin = 0;
     if (cudaFuncGetAttributes(&fa, k_gemv_umma) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemv_umma: attributes");
-    const size_t room = (size_t)optin - fa.sharedSizeBytes - 1024;        // 1 KB: alignment of the dynamic part
+    const size_t room = (size_t)optin - fa.sharedSizeBytes - 2048;    // 1 KB alignment slack + 1 KB system reserve
     if (fixed + 2 * (size_t)p.stage_bytes > room) return B200_ENOTIMPL;
     p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nst), (room - fixed) / p.stage_bytes);
+    // The scale warps look two steps ahead before they release a step: with a ring of two that
+    // would wait for itself.
+    if (p.stages < 3 && p.stages < nst) return B200_ENOTIMPL;
     p.status = device_status_ptr();
     if (!p.status) return B200_ENOTIMPL;
     p.prefetch_before_wait = stable_weights_option();
+    p.trace = nullptr;
+#ifdef B200_TRACE
+    { static unsigned long long* tb = nullptr; static int cnt = 0;
+      if (!tb) { cudaMalloc(&tb, 8 * 1024 * 64 * 8); cudaMemset(tb, 0, 8 * 1024 * 64 * 8); }
+      p.trace = tb + (size_t)(cnt++ % 8) * 1024 * 64; g_trace_umma = tb; }
+#endif
     const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
     static bool ready = false;
     if (!ready) {
-        if (cudaFuncSetAttribute(k_gemv_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(room + 1024)) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_gemv_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) != cudaSuccess)
             return launch_failed("gemv_umma: cudaFuncSetAttribute");
         ready = true;
     }
@@ -337,3 +509,11 @@ int nvfp4_multi_umma(const GemvParams& g, cudaStream_t s) {
 }
 
 }  // namespace b200
+
+#ifdef B200_TRACE
+extern "C" int b200_debug_trace_umma(unsigned long long* host_out, int n_cta) {
+    if (!b200::g_trace_umma) return 1;    // all 8 launch regions of 1024 CTAs x 64 slots
+    (void)n_cta;
+    return cudaMemcpy(host_out, b200::g_trace_umma, (size_t)8 * 1024 * 64 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
+}
+#endif

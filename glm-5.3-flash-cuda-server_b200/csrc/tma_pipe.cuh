@@ -11,7 +11,7 @@
 namespace b200 {
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;          // polls; each poll may block for a HW time slice
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;   // and never longer than about a second
+constexpr long long WAIT_LIMIT_NS = 1000000000ll;   // and never longer than about a second
 
 // A kernel receives `status`, the address of the library's device status word: 0 = no wait has
 // ever given up; otherwise (code << 16 | blockIdx.x & 0xffff) of the first one that did.
@@ -45,10 +45,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && global_ns() - t0 > WAIT_LIMIT_NS) break;
+        if (mbar_try_wait(bar, parity)) return true;   // try_wait itself suspends the thread for a HW time slice
+        if (i > 256u) __nanosleep(100);               // a long wait: leave the issue slots to the warps that have work
+        // %globaltimer is not strictly monotonic between reads: compare as a SIGNED difference, or a
+        // backward tick looks like a wait of 2^64 ns.
+        if ((i & 63u) == 63u && (long long)(global_ns() - t0) > WAIT_LIMIT_NS) break;
     }
     atomicCAS(status, 0u, (code << 16) | (blockIdx.x & 0xffffu));
+    atomicOr(status + 1, 1u << code);
+    return false;
+}
+// The same bounded wait with a non-blocking poll (mbarrier.test_wait): try_wait parks the thread
+// for a hardware time slice, which costs wake-up latency on a critical path.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, unsigned* status, unsigned code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0; i < (SPIN_LIMIT << 4); ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (i > 4096u) __nanosleep(64);
+        if ((i & 255u) == 255u && (long long)(global_ns() - t0) > WAIT_LIMIT_NS) break;
+    }
+    atomicCAS(status, 0u, (code << 16) | (blockIdx.x & 0xffffu));
+    atomicOr(status + 1, 1u << code);
     return false;
 }
 // global -> shared bulk copy; dst, src 16-byte aligned, bytes a multiple of 16.

@@ -156,9 +156,11 @@ def test_gemm_rows_equal_gemv_bitwise():
 
 
 def test_pipelined_and_general_kernels_agree_bitwise(monkeypatch):
-    """M = 1 with K % 256 == 0 runs the bulk-copy pipelined kernel; everything else runs the
+    """The two CUDA-core kernels (the fallback path when the tensor-core kernel cannot take a
+    shape): M = 1 with K % 256 == 0 runs the bulk-copy pipelined kernel, everything else the
     general kernel.  Both must give the same bits, or a gemm row would differ from its gemv."""
     P = pkg()
+    monkeypatch.setenv('B200_NVFP4_UMMA', '0')
     for (N, K) in [(12288, 4096), (1000, 4096), (700, 1536), (515, 256), (4096, 2048)]:
         W = dev_weight(host_triple((min(N, 1024), K), N + K)) if N <= 1024 else P.quantize(
             (torch.randn((N, K), device='cuda') * 0.02).to(torch.bfloat16))
@@ -171,6 +173,77 @@ def test_pipelined_and_general_kernels_agree_bitwise(monkeypatch):
         assert torch.equal(a, b), (N, K)
         assert (a != 0).float().mean() > 0.9
     assert P.device_status() == 0
+
+
+# ---- tensor-core kernel (K % 256 == 0, 16-byte aligned operands) ------------------------------------
+
+@pytest.mark.parametrize('N,K,M', [(512, 256, 1), (1000, 4096, 1), (4096, 1024, 3), (700, 1536, 8), (32, 4096, 1),
+                                   (64, 2048, 5), (300, 16384, 8), (300, 12288, 1), (20000, 512, 2), (129, 7168, 4)])
+def test_tensor_core_gemv_vs_oracle_and_row_invariance(N, K, M):
+    """Every shape class of the tensor-core kernel: several steps per stage (K up to 16384, where
+    the activation rows are taken in chunks), swizzled and plain scale slabs (K/16 a multiple of
+    128 or not), row tiles of 8..128, more tiles than SMs.  Each row must also equal the
+    single-row call bit for bit, whatever chunking or tile height the batched call used."""
+    P, O = pkg(), oracle()
+    t = host_triple((N, K), N + K + M)
+    W = dev_weight(t)
+    x = np.random.default_rng(N + M).normal(0, 1, (M, K)).astype(np.float32)
+    x[M - 1] *= 37.0
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((M, N), float('nan'), device='cuda')
+    P.gemm(W, xd, y)
+    ref = O.gemm(x, *t)
+    for m in range(M):
+        assert O.rel_l2(y[m].cpu().numpy(), ref[m]) <= REL_TOL, m
+        y1 = torch.full((1, N), float('nan'), device='cuda')
+        P.gemm(W, xd[m:m + 1].contiguous(), y1)
+        assert torch.equal(y[m], y1[0]), m
+    assert P.device_status() == 0
+
+
+def test_tensor_core_and_cuda_core_kernels_agree_within_tolerance(monkeypatch):
+    """Not bit for bit (the tensor-core kernel rounds activations to 14 fractional bits of the
+    row maximum, the CUDA-core kernels to fp16): both within the tolerance of the oracle, and of
+    one another."""
+    P, O = pkg(), oracle()
+    t = host_triple((777, 2048), 5)
+    W = dev_weight(t)
+    x = torch.randn(3, 2048, device='cuda')
+    a = P.gemm(W, x).cpu().numpy()
+    monkeypatch.setenv('B200_NVFP4_UMMA', '0')
+    b = P.gemm(W, x).cpu().numpy()
+    assert not np.array_equal(a, b)                  # two different kernels did run
+    assert O.rel_l2(a, b) <= REL_TOL
+    ref = O.gemm(x.cpu().numpy(), *t)
+    assert O.rel_l2(a, ref) < O.rel_l2(b, ref)       # and the tensor-core one is the finer of the two
+
+
+def test_tensor_core_kernel_in_a_cuda_graph_chain():
+    """Back-to-back launches without host gaps (graph replay, programmatic dependent launch): a
+    late asynchronous barrier arrival of one CTA must not land in the next CTA's shared memory."""
+    P = pkg()
+    Ws = [P.quantize((torch.randn((4096, 4096), device='cuda') * 0.02).to(torch.bfloat16)) for _ in range(3)]
+    x = torch.randn(1, 4096, device='cuda')
+    want = [P.gemm(W, x) for W in Ws]
+    ys = [torch.empty_like(w) for w in want]
+    P.set_option(P.OPT_STABLE_WEIGHTS, 1)
+    try:
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            for _ in range(2):                       # warm-up on the capture stream
+                for W, y in zip(Ws, ys): P.gemm(W, x, y)
+            st.synchronize()
+            with torch.cuda.graph(g, stream=st):
+                for _ in range(8):
+                    for W, y in zip(Ws, ys): P.gemm(W, x, y)
+        for _ in range(5): g.replay()
+        torch.cuda.synchronize()
+    finally:
+        P.set_option(P.OPT_STABLE_WEIGHTS, 0)
+    assert P.device_status() == 0
+    for y, w in zip(ys, want): assert torch.equal(y, w)
 
 
 def test_gemv_run_to_run_identical():
