@@ -63,14 +63,17 @@ def lib():
         L.b200_moe_experts.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
         L.b200_moe_forward_static.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, ci, vp]
         L.b200_moe_static_ws_limit.restype = st
+        L.b200_moe_prepare.argtypes = [C.POINTER(MoeLayerC)]
+        L.b200_moe_release.argtypes = [C.POINTER(MoeLayerC)]
         _lib = L
     return _lib
 
 
+ENOTIMPL = 6
 EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
            'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
-           'b200_moe_forward_static', 'b200_moe_static_ws_limit']
+           'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release']
 
 
 def check(rc, what):
@@ -246,6 +249,20 @@ def moe_forward(layer, x, y=None, sel=None, wts=None, stream=None):
     ws = layer.workspace(M)
     check(lib().b200_moe_forward(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), _ptr(ws), M, stream_ptr(stream)), 'b200_moe_forward')
     return y, sel, wts
+
+
+def moe_prepare(layer):
+    """Build the layer's TMA descriptors so that batches of up to 8 tokens run on the tensor-core
+    kernels.  Returns False when the geometry does not suit them (the layer keeps the CUDA-core path)."""
+    rc = lib().b200_moe_prepare(C.byref(layer.c))
+    if rc == ENOTIMPL:
+        return False
+    check(rc, 'b200_moe_prepare')
+    return True
+
+
+def moe_release(layer):
+    check(lib().b200_moe_release(C.byref(layer.c)), 'b200_moe_release')
 
 
 def moe_experts(layer, x, sel, wts, y=None, stream=None):

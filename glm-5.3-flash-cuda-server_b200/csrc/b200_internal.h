@@ -39,5 +39,17 @@ int nvfp4_math_mode();
 int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
 // gemv_umma.cu: single-row tensor-core (tcgen05 block-scaled) kernel; same contract.
 int nvfp4_multi_umma(const GemvParams& p, int M, cudaStream_t s);
+// One job of the tensor-core kernel: x [M, K], y [M, N].  x2 != nullptr: the activations are the
+// clamped SwiGLU of two vectors, x = silu(min(x, limit)) * clamp(x2, -limit, limit) (the MoE down
+// projection reads the gate and up products directly).  mw, ms: CUtensorMap of packed weights and
+// of scales in GLOBAL memory (job-table launches); nullptr = the maps passed as kernel parameters.
+struct UmJob { float* y; const float* x; const float* x2; const float* gs; const void* mw; const void* ms; int N; int M; int task0; int pad; };
+bool umma_shape_ok(int K);
+// moe_umma.cu: the experts of a prepared layer on the tensor-core kernel; B200_ENOTIMPL = not applicable.
+size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M);
+int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                     void* scratch, int M, cudaStream_t s);
+int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, cudaStream_t s);
 
 }  // namespace b200

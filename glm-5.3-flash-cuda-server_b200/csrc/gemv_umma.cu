@@ -59,11 +59,12 @@ constexpr int UM_TMEM_COLS = 512;                  // D0..D3 [0,256), 64 each | 
 constexpr int UM_COL_SB = 256, UM_COL_SF = 272;
 
 
-struct UmJob { float* y; const float* x; const float* gs; int N; int M; int task0; };     // x [M, K], y [M, N]
 struct UmParams {
     UmJob j[B200_GEMV_MULTI_MAX];
+    const UmJob* table;                            // != nullptr: jobs live in global memory, tiles_per_job CTAs each
     unsigned int* status;
-    int n_jobs, K, R, stages, prefetch_before_wait, max_m;
+    float limit;                                   // SwiGLU clamp for jobs with x2
+    int n_jobs, K, R, stages, prefetch_before_wait, max_m, tiles_per_job;
     uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
     int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
     unsigned long long* trace;                     // B200_TRACE builds only: 64 timestamps per CTA
@@ -124,9 +125,18 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     const int K = p.K, nst = K >> 8;               // 256-k steps along K
     // which job / rows
     int ji = 0;
-    #pragma unroll
-    for (int q = 1; q < B200_GEMV_MULTI_MAX; ++q) if (q < p.n_jobs && (int)blockIdx.x >= p.j[q].task0) ji = q;
-    const UmJob J = p.j[ji];
+    UmJob J;
+    if (p.table) {
+        pdl_wait();                                  // the table is written by an earlier kernel of the stream
+        ji = (int)blockIdx.x / p.tiles_per_job;
+        J = p.table[ji];
+        J.task0 = ji * p.tiles_per_job;
+    } else {
+        #pragma unroll
+        for (int q = 1; q < B200_GEMV_MULTI_MAX; ++q) if (q < p.n_jobs && (int)blockIdx.x >= p.j[q].task0) ji = q;
+        J = p.j[ji];
+        J.mw = &maps.w[ji]; J.ms = &maps.s[ji];
+    }
     const int row0 = ((int)blockIdx.x - J.task0) * p.R;
     const int valid = min(p.R, J.N - row0);
     const int M = J.M;
@@ -160,8 +170,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         // One thread issuing tensor loads back to back gets one out every ~0.35 us (measured), so
         // the steps are dealt to the lanes: each lane waits for its own stage and issues on its own.
         if (warp == 0) {
-            if (lane == 0) { UTRACE(0); asm volatile("prefetch.tensormap [%0];" :: "l"(&maps.w[ji]) : "memory");
-                             asm volatile("prefetch.tensormap [%0];" :: "l"(&maps.s[ji]) : "memory"); }
+            if (lane == 0) { UTRACE(0); asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
+                             asm volatile("prefetch.tensormap [%0];" :: "l"(J.ms) : "memory"); }
             if (!p.prefetch_before_wait) pdl_wait();
             // All scale rows of the CTA first, in slabs [R rows x sc_box bytes]: one tensor load per
             // slab instead of one [R x 16 B] box per step (a box costs the TMA unit ~1 ns per row
@@ -171,7 +181,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), (uint32_t)p.R * (uint32_t)(K >> 4));
             __syncwarp();
             if (lane < nslab)
-                tma_load_2d(smem_u32(scl) + (uint32_t)lane * (uint32_t)p.R * (uint32_t)p.sc_box, &maps.s[ji], lane * p.sc_box, row0, smem_u32(&sc_bar));
+                tma_load_2d(smem_u32(scl) + (uint32_t)lane * (uint32_t)p.R * (uint32_t)p.sc_box, (const CUtensorMap*)J.ms, lane * p.sc_box, row0, smem_u32(&sc_bar));
             const uint32_t bytes = (uint32_t)p.R * 128u;
             const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), ring0 = smem_u32(ring);
             for (int it = lane; it < nst; it += 32) {
@@ -179,7 +189,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 if (it >= p.stages) UM_WAIT(empty0 + (it - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
                 const uint32_t bar = full0 + it * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
                 mbar_expect_tx(bar, bytes);
-                tma_load_2d(dst, &maps.w[ji], it * 128, row0, bar);
+                tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0, bar);
                 if (it == 0) UTRACE(1);
             }
             __syncwarp();
@@ -243,16 +253,30 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         pdl_wait();
         if (t4 == 0) UTRACE(32);
         const float* x = J.x;
+        const float* x2 = J.x2;
+        const float lim = p.limit;
+        auto ldx = [&](const float4* row, const float4* row2, int i) -> float4 {
+            float4 v = row[i];
+            if (row2) {
+                const float4 u = row2[i];
+                const float g[4] = {fminf(v.x, lim), fminf(v.y, lim), fminf(v.z, lim), fminf(v.w, lim)};
+                const float w[4] = {fminf(fmaxf(u.x, -lim), lim), fminf(fmaxf(u.y, -lim), lim), fminf(fmaxf(u.z, -lim), lim), fminf(fmaxf(u.w, -lim), lim)};
+                v = make_float4((g[0] / (1.f + __expf(-g[0]))) * w[0], (g[1] / (1.f + __expf(-g[1]))) * w[1],
+                                (g[2] / (1.f + __expf(-g[2]))) * w[2], (g[3] / (1.f + __expf(-g[3]))) * w[3]);
+            }
+            return v;
+        };
         // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
         // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
         float4 xv[4];
         for (int m = 0; m < M; ++m) {
             const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+            const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
             float a = 0.f;
             for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
                 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const float4 v = xr[i + q];
+                    const float4 v = ldx(xr, xr2, i + q);
                     if (i == t4 * 4) xv[q] = v;
                     a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
@@ -270,13 +294,14 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             const float inv = 16384.f / gamma;
             if (t4 < UM_NB) gam[m][t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
             const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+            const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
             for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
                 // 16 activations -> 16 words of eight e2m1 codes (nibble j = digit of weight 4^-(7-j)),
                 // then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
                 uint32_t W[16];
                 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 f = (M == 1 && g == t4) ? xv[q4] : xr[g * 4 + q4];
+                    const float4 f = (M == 1 && g == t4) ? xv[q4] : ldx(xr, xr2, g * 4 + q4);
                     const float v[4] = {f.x, f.y, f.z, f.w};
                     #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -421,6 +446,8 @@ static bool make_map(CUtensorMap* m, const void* base, int rows, size_t row_byte
 // Conditions: M = 1 (one activation row shared by all jobs), K % 256 == 0 and K <= 16384, 16-byte
 // aligned tensors and activation, at least 256 rows in total.
 static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s);
+static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaStream_t s);
+static bool scale_box(int K, int* box, int* swz);
 
 // Rows of the activations are taken in chunks that fit the shared memory (the B image takes M KB
 // per 256 k); every chunk size computes each row with the same arithmetic, so results do not
@@ -454,17 +481,21 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     static UmMaps maps;                              // one host thread at a time calls in
     UmParams p{};
     p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = M;
-    if ((K / 16) % 128 == 0) { p.sc_box = 128; p.sc_swz = 1; }
-    else if (K / 16 <= 256) { p.sc_box = K / 16; p.sc_swz = 0; }
-    else return B200_ENOTIMPL;
+    if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
-        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, g.j[i].gs, g.j[i].N, M, tasks};
+        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr, g.j[i].N, M, tasks, 0};
         tasks += (g.j[i].N + R - 1) / R;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
     }
     for (int i = g.n_jobs; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].task0 = 0x7fffffff; maps.w[i] = maps.w[0]; maps.s[i] = maps.s[0]; }
+    return umma_finish_launch(p, maps, tasks, s);
+}
+
+// Everything after the jobs are known: shared-memory budget, stage count, launch.
+static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaStream_t s) {
+    const int K = p.K, R = p.R, M = p.max_m;
     p.stage_bytes = ((uint32_t)R * 128u + 1023u) & ~1023u;
     const int nst = K / 256;
     size_t fixed = (size_t)nst * M * 1024 + (size_t)R * (K / 16);      // B image | scale slabs
@@ -506,6 +537,34 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     lc.attrs = at; lc.numAttrs = 1;
     if (cudaLaunchKernelEx(&lc, k_gemv_umma, p, maps) != cudaSuccess) return launch_failed("k_gemv_umma");
     return check_launch("k_gemv_umma");
+}
+
+static bool scale_box(int K, int* box, int* swz) {
+    if ((K / 16) % 128 == 0) { *box = 128; *swz = 1; return true; }
+    if (K / 16 <= 256) { *box = K / 16; *swz = 0; return true; }
+    return false;
+}
+
+// ---- job-table launches (the MoE experts) ---------------------------------------------------------
+bool umma_shape_ok(int K) { int b, z; return !(K & 255) && K <= 16384 && scale_box(K, &b, &z) && encode_fn(); }
+
+int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R) {
+    int box = 0, swz = 0;
+    if (!umma_shape_ok(K) || !scale_box(K, &box, &swz) || ((uintptr_t)P & 15) || ((uintptr_t)S & 15)) return B200_ENOTIMPL;
+    if (!make_map(static_cast<CUtensorMap*>(out_w), P, N, (size_t)K / 2, 128, R, true) ||
+        !make_map(static_cast<CUtensorMap*>(out_s), S, N, (size_t)K / 16, box, R, swz != 0)) return B200_ENOTIMPL;
+    return B200_OK;
+}
+
+// n_jobs single-row jobs of N rows each, described by `table` (device memory, filled by an earlier
+// kernel of the stream); every job's tensor maps were encoded with box height R.
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, cudaStream_t s) {
+    static UmMaps none{};                            // unused in table mode, still a kernel parameter
+    UmParams p{};
+    p.table = table; p.limit = limit; p.n_jobs = n_jobs; p.K = K; p.R = R; p.max_m = 1;
+    p.tiles_per_job = (N + R - 1) / R;
+    if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
+    return umma_finish_launch(p, none, n_jobs * p.tiles_per_job, s);
 }
 
 }  // namespace b200

@@ -191,7 +191,11 @@ static int grid_for(Kern kern, size_t smem, int tasks, int* grid) {
 }
 
 static int experts_forward(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
-                           const float* wts, float* act, int M, cudaStream_t s) {
+                           const float* wts, float* act, int M, cudaStream_t s, bool allow_tensor_path) {
+    if (allow_tensor_path) {                             // prepared layers, up to 8 tokens (moe_umma.cu)
+        const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s);
+        if (rc != B200_ENOTIMPL) return rc;
+    }
     MoeArgs a{};
     a.x = x; a.y = y; a.sel = sel; a.wts = wts; a.act = act;
     a.experts = L->experts; a.shared = L->shared;
@@ -232,10 +236,17 @@ static int experts_forward(const float* x, const b200_moe_layer* L, float* y, co
 
 using namespace b200;
 
-// Workspace: logits f32 [M, E] | act f32 [M, topk+1, inter], each part 256-byte aligned.
+// Workspace: logits f32 [M, E] | scratch of the experts, each part 256-byte aligned.  The scratch is
+// act f32 [M, topk+1, inter] for the CUDA-core experts; the tensor-core path (up to 8 tokens) wants
+// more (moe_umma.cu), and the size covers whichever of the two a call may take.
+static size_t legacy_workspace_bytes(const b200_moe_layer* L, int M) {
+    return align_up((size_t)M * L->n_expert * 4, 256) + align_up((size_t)M * (L->topk + 1) * L->inter * 4, 256);
+}
 extern "C" size_t b200_moe_workspace_bytes(const b200_moe_layer* L, int M) {
     if (!L || M < 1) return 0;
-    return align_up((size_t)M * L->n_expert * 4, 256) + align_up((size_t)M * (L->topk + 1) * L->inter * 4, 256);
+    size_t scratch = align_up((size_t)M * (L->topk + 1) * L->inter * 4, 256);
+    if (M <= 8) scratch = std::max(scratch, moe_umma_ws_bytes(L, M));
+    return align_up((size_t)M * L->n_expert * 4, 256) + scratch;
 }
 
 extern "C" int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts,
@@ -254,7 +265,7 @@ extern "C" int b200_moe_experts(const float* x, const b200_moe_layer* L, float* 
     if (!x || !y || !sel || !wts || !ws) return B200_EINVAL;
     if ((uintptr_t)ws & 15) return B200_EALIGN;
     float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));
-    return experts_forward(x, L, y, sel, wts, act, M, stream);
+    return experts_forward(x, L, y, sel, wts, act, M, stream, true);
 }
 
 extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
@@ -312,7 +323,7 @@ extern "C" size_t b200_moe_static_ws_limit(void) { return B200_MOE_STATIC_WS_BYT
 extern "C" int b200_moe_forward_static(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
                                        float* wts, int M, b200_stream stream) {
     if (int rc = check_layer(L, M)) return rc;
-    const size_t need = b200_moe_workspace_bytes(L, M);
+    const size_t need = legacy_workspace_bytes(L, M);    // this entry point always runs the CUDA-core experts
     if (need > B200_MOE_STATIC_WS_BYTES) {
         fprintf(stderr, "b200_nvfp4: b200_moe_forward_static needs %zu bytes of scratch for M=%d, the built-in "
                         "workspace holds %zu; use b200_moe_forward with a caller-allocated workspace\n",
@@ -321,5 +332,9 @@ extern "C" int b200_moe_forward_static(const float* x, const b200_moe_layer* L, 
     }
     void* ws = nullptr;
     if (int rc = moe_static_ws_ptr(&ws)) return rc;
-    return b200_moe_forward(x, L, y, sel, wts, ws, M, stream);
+    if (!x || !y || !sel || !wts) return B200_EINVAL;
+    float* logits = static_cast<float*>(ws);
+    if (int rc = b200_moe_route(x, L, sel, wts, logits, M, stream)) return rc;
+    float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));
+    return experts_forward(x, L, y, sel, wts, act, M, stream, false);
 }

@@ -137,6 +137,19 @@ int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float*
 int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
                      float* wts, void* ws, int M, b200_stream stream);
 
+/* Optional, once per layer after its weights are on the device: lets b200_moe_forward and
+ * b200_moe_experts run batches of up to 8 tokens on the tensor-core kernels.  It reads the layer's
+ * device-side expert tables (a synchronous copy: call it at load time, never under stream
+ * capture), encodes TMA descriptors for every expert and keeps them in device memory until
+ * b200_moe_release or process exit.  The layer is recognised later by its experts / shared
+ * pointers and geometry, so the tables and the weights must stay where they are.  Returns
+ * B200_ENOTIMPL when the geometry or alignment does not suit those kernels (hidden and inter
+ * multiples of 256, 16-byte aligned tensors); the layer then keeps using the CUDA-core kernels,
+ * as does every layer that was never prepared.  No counterpart in the reference, whose engine
+ * builds its tables at load (src/engine.cu:168-195) -- the natural place to call this. */
+int b200_moe_prepare(const b200_moe_layer* L);
+int b200_moe_release(const b200_moe_layer* L);
+
 /* Expert half only, routing supplied by the caller (sel/wts are inputs).  No counterpart in
  * the reference, which always routes itself; used where routing is decided elsewhere. */
 int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
@@ -146,8 +159,10 @@ int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const in
  * whose buffers were sized at start-up by the reference's own moe_workspace_floats(), and which
  * may not call cudaMalloc later (it would synchronise the device in the middle of the token
  * loop, and is illegal under stream capture).  The scratch is a 1 MiB array inside the library
- * (b200_moe_static_ws_limit()), held by every GPU that loads the library until exit; a layer /
- * M whose b200_moe_workspace_bytes exceeds it is refused with B200_ELIMIT.  The call allocates
+ * (b200_moe_static_ws_limit()), held by every GPU that loads the library until exit; it holds the
+ * router logits [M, n_expert] and the activations [M, topk + 1, inter] (f32, each part rounded up
+ * to 256 bytes), and a layer / M that needs more is refused with B200_ELIMIT.  This entry point
+ * always runs the CUDA-core expert kernels, prepared layer or not.  The call allocates
  * nothing.  The FIRST call on each device looks the array's device address up
  * (cudaGetSymbolAddress) -- make that call before any stream capture.  All calls on a device
  * share the array and it keeps the last call's contents; nothing in it needs clearing, but two

@@ -135,6 +135,41 @@ def test_moe_full_geometry(I):
             assert O.rel_l2(y4[:M].cpu().numpy(), yr.cpu().numpy()) <= REL_TOL
 
 
+@pytest.mark.parametrize('H,I,E,M,shared', [(1024, 512, 32, 1, True), (1024, 512, 32, 5, False), (4096, 1536, 144, 1, True),
+                                            (4096, 1536, 144, 8, True), (4096, 2048, 144, 4, True)])
+def test_moe_prepared_layer_runs_tensor_core_experts(H, I, E, M, shared):
+    """After b200_moe_prepare the experts of up to 8 tokens run on the tensor-core kernel: same
+    routing, output within tolerance of the oracle and of the CUDA-core experts, each token equal
+    to that token alone bit for bit, expert half alone equal to the whole block, run to run equal."""
+    P, O = pkg(), oracle()
+    layer, d = build_layer(H, I, E, 8, seed=70 + M, shared=shared, on_gpu=H > 1024)
+    x = np.random.default_rng(M + I).normal(0, 1, (M, H)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y_cc, sel_cc, _ = P.moe_forward(layer, xd)
+    assert P.moe_prepare(layer)
+    try:
+        y, sel, wts = check_layer(layer, d, x)
+        assert torch.equal(sel, sel_cc)
+        assert not torch.equal(y, y_cc)              # a different kernel did run
+        assert O.rel_l2(y.cpu().numpy(), y_cc.cpu().numpy()) <= REL_TOL
+        for m in range(M):
+            y1, sel1, wts1 = P.moe_forward(layer, xd[m:m + 1].contiguous())
+            assert torch.equal(y1[0], y[m]) and torch.equal(sel1[0], sel[m]) and torch.equal(wts1[0], wts[m]), m
+        assert torch.equal(P.moe_experts(layer, xd, sel, wts), y)
+        assert torch.equal(P.moe_forward(layer, xd)[0], y)
+        assert P.device_status() == 0
+    finally:
+        P.moe_release(layer)
+    y_after, _, _ = P.moe_forward(layer, xd)          # released: the CUDA-core experts again
+    assert torch.equal(y_after, y_cc)
+
+
+def test_moe_prepare_refuses_unsuitable_geometry():
+    P = pkg()
+    layer, _ = build_layer(1056, 544, 8, 2, seed=3)   # not multiples of 256
+    assert P.moe_prepare(layer) is False
+
+
 def test_route_ties_lowest_index_wins():
     """Two experts with identical router rows and biases tie exactly; the lower index must be
     ranked first (reference kernels/moe.cu:146-152)."""

@@ -52,8 +52,10 @@ def test_static_workspace_refuses_oversized_requests():
     layer, _ = build_layer(1024, 512, 32, 8, seed=9)
     limit = P.lib().b200_moe_static_ws_limit()
     assert limit == 1 << 20
-    need_per_token = P.lib().b200_moe_workspace_bytes(C.byref(layer.c), 1)
-    M = int(limit // need_per_token) + 8
+    # this entry point's scratch: logits [M, E] + activations [M, topk + 1, inter], f32, 256-byte aligned parts
+    up = lambda v: (v + 255) // 256 * 256
+    need = lambda M: up(M * 32 * 4) + up(M * 9 * 512 * 4)
+    M = next(m for m in range(1, 1 << 12) if need(m) > limit) + 8
     x = torch.zeros((M, 1024), device='cuda')
     with pytest.raises(P.B200Error, match='documented maximum'):
         P.moe_forward_static(layer, x)
