@@ -28,6 +28,16 @@ import time
 import numpy as np
 import torch
 
+UMMA = os.environ.get('B200_NVFP4_UMMA') != '0'          # the library's default path; '0' times the CUDA-core kernels
+if UMMA:
+    DTYPE = 'nvfp4 weights (e2m1 + e4m3 block scales) x activations as eight e2m1 digit columns (14 fractional bits of the row maximum), fp32 accumulate'
+    MATH = 'tcgen05.mma kind::mxf4nvf4.block_scale.block16, accumulators in TMEM'
+    KERNEL = 'k_gemv_umma'
+else:
+    DTYPE = 'nvfp4 weights (e2m1 + e4m3 scales), f16 products, f32 accumulate'
+    MATH = 'fp32-mac' if os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'
+    KERNEL = 'k_gemv_tma'
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as G  # noqa: E402
@@ -210,7 +220,11 @@ def build_moe_layers(P, n_layers, H, I, E, topk, seed):
     return layers
 
 
-def bench_moe(P, layers, M, steps, warmup):
+def bench_moe(P, layers, M, steps, warmup, prepare=True):
+    """prepare: build the layers' TMA descriptors first (b200_moe_prepare), so that the experts run on
+    the tensor-core kernel; False times the CUDA-core experts."""
+    for L in layers:
+        if prepare: P.moe_prepare(L)
     H, I, E, topk = layers[0].hidden, layers[0].inter, layers[0].n_expert, layers[0].topk
     gen = torch.Generator(device='cuda').manual_seed(77)
     xs = [torch.randn((M, H), generator=gen, device='cuda') for _ in range(8)]
@@ -223,6 +237,8 @@ def bench_moe(P, layers, M, steps, warmup):
         fns[-1](); torch.cuda.synchronize()
         distinct.append(len(set(sel.cpu().numpy().ravel().tolist())))
     ms = time_steps(fns, steps, warmup)
+    for L in layers:
+        if prepare: P.moe_release(L)
     per_expert = 3 * nv_bytes(I, H)
     d = float(np.mean(distinct))
     nbytes = (d + 1) * per_expert + E * H * 2 + E * 4 + 2 * M * H * 4 + M * topk * 8
@@ -414,11 +430,12 @@ def main():
                                        'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
     if want('moe'):
         layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4000)
-        for M in (1, 4):
-            m, b, d = bench_moe(P, layers, M, sub_steps, a.warmup)
-            sub['moe_layer_I1536_M%d' % M] = {'us_per_layer': m * 1e3, 'bytes': b, 'distinct_routed': d,
-                                              'tbps': b / (m * 1e-3) / 1e12,
-                                              'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+        for M, prep in ((1, True), (4, True), (8, True), (1, False)):
+            m, b, d = bench_moe(P, layers, M, sub_steps, a.warmup, prep)
+            sub['moe_layer_I1536_M%d%s' % (M, '' if prep else '_cuda_core')] = {
+                'us_per_layer': m * 1e3, 'bytes': b, 'distinct_routed': d, 'tbps': b / (m * 1e-3) / 1e12,
+                'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak,
+                'experts': 'tensor-core (prepared layer)' if prep else 'CUDA-core'}
         del layers
     if want('quant'):
         m, b = bench_quantize(P, min(sub_steps, 200), a.warmup)
@@ -428,13 +445,13 @@ def main():
     out = {
         'metric': 'nvfp4_gemv_hbm_tbps', 'value': value, 'unit': 'TB/s', 'n_gpus': 1, 'steps': a.steps,
         'warmup': a.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
-        'vs_baseline': None, 'dtype': 'nvfp4 weights (e2m1 + e4m3 scales), f16 products, f32 accumulate',
+        'vs_baseline': None, 'dtype': DTYPE,
         'data': 'synthetic',
         'config': {'workload': 'six fused sibling NVFP4 gemvs sharing one input, K=4096, N=[4096,4096,4096,512,64,32], M=1 (configs[1])',
                    'l2': 'inputs larger than L2: step i reads weight copy i mod %d (%.0f MB in rotation)' % (copies, copies * nbytes / 1e6),
                    'launch': 'steps captured back to back in CUDA graphs; programmatic dependent launch; weights declared stable',
-                   'math': 'fp32-mac' if P.lib() and os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'},
-        'roofline': {'bound': 'hbm', 'kernel': 'k_gemv_nvfp4<1,4>', 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
+                   'math': MATH},
+        'roofline': {'bound': 'hbm', 'kernel': KERNEL, 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
                      'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': None,
                      'algorithmic_bytes_per_launch': nbytes},
         'e2e': {'value': nbytes / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,

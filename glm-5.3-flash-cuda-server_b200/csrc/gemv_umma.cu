@@ -65,6 +65,7 @@ struct UmParams {
     unsigned int* status;
     float limit;                                   // SwiGLU clamp for jobs with x2
     int n_jobs, K, R, stages, prefetch_before_wait, max_m, tiles_per_job;
+    int T;                                         // consecutive row tiles of one job per CTA (T * max_m <= 8, T * K/256 <= 64)
     uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
     int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
     unsigned long long* trace;                     // B200_TRACE builds only: 64 timestamps per CTA
@@ -126,31 +127,33 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     // which job / rows
     int ji = 0;
     UmJob J;
+    const int T = p.T;
     if (p.table) {
         pdl_wait();                                  // the table is written by an earlier kernel of the stream
-        ji = (int)blockIdx.x / p.tiles_per_job;
+        const int per_job = p.tiles_per_job / T;     // CTAs per job (the host makes T divide tiles_per_job)
+        ji = (int)blockIdx.x / per_job;
         J = p.table[ji];
-        J.task0 = ji * p.tiles_per_job;
+        J.task0 = ji * per_job;
     } else {
         #pragma unroll
         for (int q = 1; q < B200_GEMV_MULTI_MAX; ++q) if (q < p.n_jobs && (int)blockIdx.x >= p.j[q].task0) ji = q;
         J = p.j[ji];
         J.mw = &maps.w[ji]; J.ms = &maps.s[ji];
     }
-    const int row0 = ((int)blockIdx.x - J.task0) * p.R;
-    const int valid = min(p.R, J.N - row0);
+    const int row0 = ((int)blockIdx.x - J.task0) * p.R * T;      // first row of the CTA's T tiles
+    const int nsteps = T * nst;                      // step g: tile g / nst, 256-k block g % nst
     const int M = J.M;
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);      // SWIZZLE_128B tiles need 1 KB alignment
     unsigned char* bimg = ring + (size_t)p.stages * p.stage_bytes;          // nst tiles of max_m KB: [step][row m][digit t][128 B]
-    unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: slabs [R x sc_box]
+    unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: per tile, slabs [R x sc_box]
 
     pdl_launch_dependents();
     if (tid == 0) UTRACE(3);
     if (warp >= UM_LOAD_WARPS + UM_MMA_WARPS) {      // barrier init spread over the worker threads
         const int i = tid - UM_LOADERS - 32 * UM_MMA_WARPS;
-        if (i < nst) mbar_init(smem_u32(&full_bar[i]), 1);
-        else if (i >= 64 && i < 64 + nst) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
-        else if (i >= 128 && i < 128 + nst) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
+        if (i < nsteps) mbar_init(smem_u32(&full_bar[i]), 1);
+        else if (i >= 64 && i < 64 + nsteps) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
+        else if (i >= 128 && i < 128 + nsteps) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
         else if (i == 192) mbar_init(smem_u32(&done_bar), UM_MMA_WARPS);
         else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
         mbar_fence_init();
@@ -178,32 +181,36 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // whatever the row's width).  128-byte slabs are stored 128B-swizzled, so that 32 lanes
             // reading the same 16-byte column of 32 consecutive rows hit different banks.
             const int nslab = (K >> 4) / p.sc_box;
-            if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), (uint32_t)p.R * (uint32_t)(K >> 4));
+            const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
+            if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), slab_bytes * (uint32_t)T);
             __syncwarp();
-            if (lane < nslab)
-                tma_load_2d(smem_u32(scl) + (uint32_t)lane * (uint32_t)p.R * (uint32_t)p.sc_box, (const CUtensorMap*)J.ms, lane * p.sc_box, row0, smem_u32(&sc_bar));
+            for (int q = lane; q < T * nslab; q += 32) {
+                const int t = q / nslab, sl = q - t * nslab;
+                tma_load_2d(smem_u32(scl) + (uint32_t)t * slab_bytes + (uint32_t)sl * (uint32_t)p.R * (uint32_t)p.sc_box,
+                            (const CUtensorMap*)J.ms, sl * p.sc_box, row0 + t * p.R, smem_u32(&sc_bar));
+            }
             const uint32_t bytes = (uint32_t)p.R * 128u;
             const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), ring0 = smem_u32(ring);
-            for (int it = lane; it < nst; it += 32) {
-                const int s = it % p.stages;
-                if (it >= p.stages) UM_WAIT(empty0 + (it - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
-                const uint32_t bar = full0 + it * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
+            for (int g = lane; g < nsteps; g += 32) {
+                const int s = g % p.stages, t = g / nst, it = g - t * nst;
+                if (g >= p.stages) UM_WAIT(empty0 + (g - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
+                const uint32_t bar = full0 + g * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
                 mbar_expect_tx(bar, bytes);
-                tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0, bar);
-                if (it == 0) UTRACE(1);
+                tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0 + t * p.R, bar);
+                if (g == 0) UTRACE(1);
             }
             __syncwarp();
             if (lane == 0) UTRACE(2);
             // Tail: the tcgen05.commit arrivals on empty_bar are asynchronous.  Wait for the last one
             // of every stage, or the CTA could exit with an arrival still in flight and it would
             // land on whatever the next CTA keeps at that shared-memory address.
-            for (int it = max(0, nst - p.stages) + lane; it < nst; it += 32)
-                UM_WAIT(empty0 + it * 8, 0, p.status, 5);
+            for (int g = max(0, nsteps - p.stages) + lane; g < nsteps; g += 32)
+                UM_WAIT(empty0 + g * 8, 0, p.status, 5);
             __syncwarp();
             if (lane == 0) UTRACE(62);
         }
     } else if (warp < UM_LOAD_WARPS + UM_MMA_WARPS) {
-        // ---- MMA issuers: warp w takes steps it with it % 4 == w, accumulator D[w] ----
+        // ---- MMA issuers: warp w takes the steps g with g % 4 == w ----
         named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // B image, unit scales and gam[] are ready
         tc_fence_after();
         {
@@ -211,14 +218,18 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             if (me == 0 && lane == 0) UTRACE(8);
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)M << 17) | ((128u >> 4) << 24);     // N = 8 M
             const uint64_t dA0 = umma_desc(smem_u32(ring), 1024, 2), dB0 = umma_desc(smem_u32(bimg), 1024, 2);
-            const uint32_t tD = tmem + me * 64, tSB = tmem + UM_COL_SB;
+            const uint32_t tSB = tmem + UM_COL_SB;
             const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             int s = me % p.stages;
-            for (int it = me; it < nst; it += UM_MMA_WARPS) {          // whole warp waits, lane 0 issues
+            for (int g = me; g < nsteps; g += UM_MMA_WARPS) {          // whole warp waits, lane 0 issues
+                const int t = g / nst, it = g - t * nst;
                 const uint32_t tsf = tmem + UM_COL_SF + (uint32_t)s * 16u;
+                // accumulator it % 4 of tile t: fixed by the k-block alone, so that the summation order of a
+                // row does not depend on which tile of the CTA it is in (or on how many tiles a CTA takes)
+                const uint32_t tD = tmem + (uint32_t)((it & 3) * 64 + t * 8 * M);
                 const uint64_t dA = dA0 + (((uint32_t)s * p.stage_bytes) >> 4), dB = dB0 + (uint32_t)(it * p.max_m) * 64u;
-                const uint32_t acc0 = it >= UM_MMA_WARPS;
-                UM_WAIT(sf0 + it * 8, 0, p.status, 3);
+                const uint32_t acc0 = it >= 4;                          // the first k-block of an accumulator starts it
+                UM_WAIT(sf0 + g * 8, 0, p.status, 3);
                 tc_fence_after();
                 if (lane == 0) {
                     #pragma unroll
@@ -228,8 +239,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                                      :: "r"(tD), "l"(dA + kb * 2), "l"(dB + kb * 2), "r"(idesc), "r"(kb ? 1u : acc0),
                                         "r"(tsf + kb * 4), "r"(tSB) : "memory");
                     }
-                    tc_commit(empty0 + it * 8);
-                    if (me == 0) UTRACE(9 + it / UM_MMA_WARPS);
+                    tc_commit(empty0 + g * 8);
+                    if (me == 0 && g < 16) UTRACE(9 + g / UM_MMA_WARPS);
                 }
                 __syncwarp();
                 s += UM_MMA_WARPS; while (s >= p.stages) s -= p.stages;
@@ -350,30 +361,34 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
             // Software-pipelined: the next step's scale bytes are read from shared memory while this
             // step's tcgen05.st is in flight.
-            auto read_scales = [&](int it, uint4 (&v)[4]) {
-                // full[it] also says that the MMAs that last read this stage's scale slot are done
-                UM_WAIT(full0 + it * 8, 0, p.status, 2);
+            const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
+            auto read_scales = [&](int g, uint4 (&v)[4]) {
+                // full[g] also says that the MMAs that last read this stage's scale slot are done
+                UM_WAIT(full0 + g * 8, 0, p.status, 2);
+                const int t = g / nst, it = g - t * nst;
+                const unsigned char* sl = scl + (uint32_t)t * slab_bytes;
+                const int valid = J.N - (row0 + t * p.R);            // rows of this tile that exist (may exceed R)
                 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int r = lane + 32 * c;
                     uint32_t off;
                     if (p.sc_swz) off = (uint32_t)(it >> 3) * (uint32_t)p.R * 128u + (uint32_t)r * 128u + (uint32_t)(((it & 7) ^ (r & 7)) << 4);
                     else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)it * 16u;
-                    v[c] = (r < valid) ? *reinterpret_cast<const uint4*>(scl + off) : make_uint4(0u, 0u, 0u, 0u);
+                    v[c] = (r < p.R && r < valid) ? *reinterpret_cast<const uint4*>(sl + off) : make_uint4(0u, 0u, 0u, 0u);
                 }
             };
             uint4 v[4], vn[4];
-            if (grp < nst) read_scales(grp, v);
-            for (int it = grp; it < nst; it += 2) {
+            if (grp < nsteps) read_scales(grp, v);
+            for (int g = grp; g < nsteps; g += 2) {
                 asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                              :: "r"(tq + UM_COL_SF + (uint32_t)s * 16u),
                                 "r"(v[0].x), "r"(v[1].x), "r"(v[2].x), "r"(v[3].x), "r"(v[0].y), "r"(v[1].y), "r"(v[2].y), "r"(v[3].y),
                                 "r"(v[0].z), "r"(v[1].z), "r"(v[2].z), "r"(v[3].z), "r"(v[0].w), "r"(v[1].w), "r"(v[2].w), "r"(v[3].w) : "memory");
-                if (it + 2 < nst) read_scales(it + 2, vn);
+                if (g + 2 < nsteps) read_scales(g + 2, vn);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
-                mbar_arrive(sf0 + it * 8);
-                if ((t4 & 127) == 0 && it < 24) UTRACE(34 + it);
+                mbar_arrive(sf0 + g * 8);
+                if ((t4 & 127) == 0 && g < 24) UTRACE(34 + g);
                 s += 2; while (s >= p.stages) s -= p.stages;
                 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = vn[c];
@@ -385,25 +400,28 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             tc_fence_after();
             if (t4 == 0) UTRACE(60);
             const int r = q4 * 32 + lane;
-            for (int m = 0; m < M; ++m) {
-                // row m of the activations: columns m*8 .. m*8+7 of each issuer's accumulator
-                uint32_t d[4][8];
-                #pragma unroll
-                for (int w = 0; w < UM_MMA_WARPS; ++w)
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=r"(d[w][0]), "=r"(d[w][1]), "=r"(d[w][2]), "=r"(d[w][3]), "=r"(d[w][4]), "=r"(d[w][5]), "=r"(d[w][6]), "=r"(d[w][7])
-                                 : "r"(tq + (uint32_t)(w * 64 + m * 8)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r < valid) {
-                    float acc = 0.f;
+            for (int t = 0; t < T; ++t) {
+                const int row = row0 + t * p.R + r;
+                for (int m = 0; m < M; ++m) {
+                    // tile t, activation row m: columns t*8M + m*8 .. +7 of each of the four accumulators
+                    uint32_t d[4][8];
                     #pragma unroll
-                    for (int t = UM_NB - 1; t >= 0; --t) {                 // small terms first
-                        float dsum = __uint_as_float(d[0][t]);
+                    for (int w = 0; w < 4; ++w)
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                     : "=r"(d[w][0]), "=r"(d[w][1]), "=r"(d[w][2]), "=r"(d[w][3]), "=r"(d[w][4]), "=r"(d[w][5]), "=r"(d[w][6]), "=r"(d[w][7])
+                                     : "r"(tq + (uint32_t)(w * 64 + t * 8 * M + m * 8)));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (r < p.R && row < J.N) {
+                        float acc = 0.f;
                         #pragma unroll
-                        for (int w = 1; w < UM_MMA_WARPS; ++w) if (w < nst) dsum += __uint_as_float(d[w][t]);   // issuers that had a step
-                        acc = fmaf(dsum, gam[m][t], acc);
+                        for (int dg = UM_NB - 1; dg >= 0; --dg) {          // small terms first
+                            float dsum = __uint_as_float(d[0][dg]);
+                            #pragma unroll
+                            for (int w = 1; w < 4; ++w) if (w < nst) dsum += __uint_as_float(d[w][dg]);   // accumulators that had a k-block
+                            acc = fmaf(dsum, gam[m][dg], acc);
+                        }
+                        J.y[(size_t)m * J.N + row] = acc / gsv;
                     }
-                    J.y[(size_t)m * J.N + row0 + r] = acc / gsv;
                 }
             }
             if (t4 == 0) UTRACE(5);
@@ -480,7 +498,7 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     }
     static UmMaps maps;                              // one host thread at a time calls in
     UmParams p{};
-    p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = M;
+    p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = M; p.T = 1;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
@@ -498,7 +516,7 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     const int K = p.K, R = p.R, M = p.max_m;
     p.stage_bytes = ((uint32_t)R * 128u + 1023u) & ~1023u;
     const int nst = K / 256;
-    size_t fixed = (size_t)nst * M * 1024 + (size_t)R * (K / 16);      // B image | scale slabs
+    size_t fixed = (size_t)nst * M * 1024 + (size_t)p.T * R * (K / 16);      // B image | scale slabs of the T tiles
     // The MMA is always 128 rows tall: it reads 16 KB from the start of a stage even when only R
     // rows were loaded (the extra accumulator rows are never stored).  Keep that read inside the
     // allocation for the last stage as well.
@@ -509,10 +527,11 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemv_umma: attributes");
     const size_t room = (size_t)optin - fa.sharedSizeBytes - 2048;    // 1 KB alignment slack + 1 KB system reserve
     if (fixed + 2 * (size_t)p.stage_bytes > room) return B200_ENOTIMPL;
-    p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nst), (room - fixed) / p.stage_bytes);
+    const int nsteps = p.T * nst;
+    p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nsteps), (room - fixed) / p.stage_bytes);
     // The scale warps look two steps ahead before they release a step: with a ring of two that
     // would wait for itself.
-    if (p.stages < 3 && p.stages < nst) return B200_ENOTIMPL;
+    if (p.stages < 3 && p.stages < nsteps) return B200_ENOTIMPL;
     p.status = device_status_ptr();
     if (!p.status) return B200_ENOTIMPL;
     p.prefetch_before_wait = stable_weights_option();
@@ -564,7 +583,17 @@ int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float
     p.table = table; p.limit = limit; p.n_jobs = n_jobs; p.K = K; p.R = R; p.max_m = 1;
     p.tiles_per_job = (N + R - 1) / R;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
-    return umma_finish_launch(p, none, n_jobs * p.tiles_per_job, s);
+    // Tiles per CTA: as many as still leave every SM a CTA.  A CTA splits its activation row and
+    // fills its pipeline once, whatever its number of tiles.  Limits: 64 steps (barriers), 8 tiles
+    // (accumulator columns), and the tiles' scale rows must fit beside four stages.
+    const int nst = K / 256, nsm = sm_count();
+    p.T = 1;
+    for (int T = 2; T <= 8; ++T) {
+        if (p.tiles_per_job % T || T * nst > UM_MAX_STEPS) continue;
+        if ((size_t)T * R * (K / 16) + (size_t)nst * 1024 + 4 * (((size_t)R * 128 + 1023) & ~(size_t)1023) > 200 * 1024) continue;
+        if ((long)n_jobs * (p.tiles_per_job / T) >= nsm - nsm / 16) p.T = T;
+    }
+    return umma_finish_launch(p, none, n_jobs * (p.tiles_per_job / p.T), s);
 }
 
 }  // namespace b200
