@@ -116,20 +116,21 @@ def capture_steps(fns):
 
 
 def time_steps(fns, steps, warmup):
-    """Runs exactly `steps` timed steps, step i being fns[i % len(fns)]: whole rotations as one
-    captured graph each, plus one shorter graph for the remainder.  Returns ms per step."""
+    """Runs exactly `steps` timed steps, step i being fns[i % len(fns)]: graphs of about a hundred
+    steps (whole rotations), plus one shorter graph for the remainder.  Returns ms per step."""
     for fn in fns:
         fn()                                        # outside capture: one-time attribute set-up
     torch.cuda.synchronize()
     R = len(fns)
-    full = capture_steps(fns)
-    rem = capture_steps(fns[:steps % R]) if steps % R else None
-    for _ in range(max(1, (warmup + R - 1) // R)):
-        full.replay()
+    G = R * max(1, min(128 // R, steps // R))          # steps per graph: whole rotations, about a hundred launches
+    full = capture_steps([fns[i % R] for i in range(G)]) if steps >= G else None
+    rem = capture_steps([fns[i % R] for i in range(steps % G)]) if steps % G else None
+    for _ in range(max(1, (warmup + G - 1) // G)):
+        (full or rem).replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps // R):
+    for _ in range(steps // G if full is not None else 0):
         full.replay()
     if rem is not None:
         rem.replay()

@@ -47,8 +47,10 @@ struct UmJob { float* y; const float* x; const float* x2; const float* gs; const
 bool umma_shape_ok(int K);
 // moe_umma.cu: the experts of a prepared layer on the tensor-core kernel; B200_ENOTIMPL = not applicable.
 size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M);
+struct MoePlan;
+int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, int M, MoePlan* q, int* R_gu, int* R_d);
 int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
-                     void* scratch, int M, cudaStream_t s);
+                     void* scratch, int M, cudaStream_t s, bool planned);
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
 int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, cudaStream_t s);
 

@@ -137,6 +137,7 @@ k_gemm_dense(float* __restrict__ y, const void* __restrict__ W, const float* __r
         const int nv = K / EPV;
         const uint4* Wr = reinterpret_cast<const uint4*>(
             static_cast<const char*>(W) + (size_t)n * K * (BF16 ? 2 : 4));
+        #pragma unroll 4                             // four weight loads in flight; the sums keep their order
         for (int i = lane; i < nv; i += 32) {
             const uint4 raw = Wr[i];
             float wf[EPV];

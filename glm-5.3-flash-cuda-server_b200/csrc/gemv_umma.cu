@@ -1,4 +1,4 @@
-// gemv_umma.cu -- NVFP4 gemv (one activation row) on the 5th-generation tensor cores:
+// gemv_umma.cu -- NVFP4 gemv / small-batch gemm (1..8 activation rows) on the 5th-generation tensor cores:
 // tcgen05.mma kind::mxf4nvf4 (block-16, UE4M3 scales), TMEM accumulators.
 //
 // Why tensor cores for a matrix-VECTOR product: the CUDA-core formulation is capped by the
@@ -17,24 +17,31 @@
 // 7.7e-6 amax(x): measured rel-L2 of a product 1.6e-5, forty times finer than fp16 staging;
 // products and sums inside the MMA are exact / fp32.
 //
-// Per CTA (one per SM): rows [r0, r0+R) of one job, R <= 128 a multiple of 8.
-//   warps 0-3   loaders: per 256-k step, cp.async (16 bytes per thread and request) of the R x 128
-//               bytes of packed weights into the 128-byte-swizzled K-major layout the MMA reads,
-//               and of the R x 16 scale bytes; stages - 1 steps are kept in flight per thread.
-//               (Tensor-map TMA boxes of R rows x 128 bytes were measured at 0.35 us per box from
-//               one CTA, 18 bytes per clock per SM: not enough to keep HBM busy.)
-//   warps 4-7   MMA issuers: warp w takes every fourth step: 4 tcgen05.mma (K = 64 each) into its
-//               own accumulator, then a tcgen05.commit frees the stage
-//   warps 8-15  workers: split the activation row into the B image (once); then, in two groups of
-//               four warps (one warp per TMEM lane quadrant) taking alternate steps, move the
-//               step's R x 16 scale bytes from shared memory to the stage's scale columns in TMEM
-//               (tcgen05.st: lane r % 32, column r / 32, the layout the block-scaled MMA reads);
+// Per CTA (one per SM): T consecutive tiles of R rows of one job (R <= 128 a multiple of 8; T = 1
+// for a plain gemv, up to 8 for the MoE job-table launches), K walked in steps of 256.
+//   warp 0      TMA producer.  First the CTA's scale rows, as slabs [R rows x 128 B] (128B-swizzled,
+//               so 32 lanes reading one 16-byte column of 32 consecutive rows hit different banks);
+//               then per step one box [128 B x R rows] of packed weights (SWIZZLE_128B, the K-major
+//               operand layout the MMA reads) into a ring of stages.  Lane l issues steps l, l+32, ..:
+//               one thread issuing tensor loads back to back gets one out every ~0.35 us (measured).
+//   warp 1      L2 prefetch of the steps the ring cannot take at once; warps 2-3 idle
+//   warps 4-7   MMA issuers: warp w takes every fourth step: 4 tcgen05.mma (K = 64 each) into the
+//               accumulator of the step's k-block (k-block % 4: the summation order of a row never
+//               depends on tiling), then a tcgen05.commit frees the stage
+//   warps 8-15  workers: split the activation rows into the B image (once per CTA); then, in two
+//               groups of four warps (one warp per TMEM lane quadrant) taking alternate steps, move
+//               the step's R x 16 scale bytes from shared memory to the stage's scale columns in
+//               TMEM (tcgen05.st: lane r % 32, column r / 32, the layout the block-scaled MMA reads);
 //               the first group finally reads the accumulators and writes y
+// Up to 8 activation rows per job: row m is columns 8m..8m+7 of the MMA's N = 8M, so every row is
+// computed exactly as if it were alone (a gemm row equals its gemv bit for bit).
 // Barriers: full[step], sf[step] and empty[step] are used once each, so that no waiter ever has
 // to tell phases apart (a parity wait cannot tell "two phases behind" from "ready").  In the
 // single-thread roles the whole warp walks the loop and waits (a lone lane whose 31 siblings are
-// parked at the closing barrier is scheduled rarely: measured 20 % slower).
-// Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast, no tensor maps.
+// parked at the closing barrier is scheduled rarely: measured 20 % slower).  Before it exits a CTA
+// waits for the last tcgen05.commit arrival of every stage: an arrival still in flight would land
+// in the shared memory of the next CTA on that SM.
+// Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast.
 #include "b200_internal.h"
 #include "nvfp4_decode.cuh"
 #include "tma_pipe.cuh"
@@ -94,28 +101,9 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Wait until at most n of this thread's cp.async groups are pending (n <= 11).
-__device__ __forceinline__ void cp_async_wait_dyn(int n) {
-    switch (n) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-    case 7: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
-    case 8: asm volatile("cp.async.wait_group 8;" ::: "memory"); break;
-    case 9: asm volatile("cp.async.wait_group 9;" ::: "memory"); break;
-    case 10: asm volatile("cp.async.wait_group 10;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 11;" ::: "memory"); break;
-    }
-}
-
+// GEN = false: the decode hot path (one activation row, one tile per CTA, jobs in the parameters,
+// plain activations) with the general loops folded away at compile time.
+template <bool GEN>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -127,8 +115,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     // which job / rows
     int ji = 0;
     UmJob J;
-    const int T = p.T;
-    if (p.table) {
+    const int T = GEN ? p.T : 1;
+    if (GEN && p.table) {
         pdl_wait();                                  // the table is written by an earlier kernel of the stream
         const int per_job = p.tiles_per_job / T;     // CTAs per job (the host makes T divide tiles_per_job)
         ji = (int)blockIdx.x / per_job;
@@ -142,7 +130,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     }
     const int row0 = ((int)blockIdx.x - J.task0) * p.R * T;      // first row of the CTA's T tiles
     const int nsteps = T * nst;                      // step g: tile g / nst, 256-k block g % nst
-    const int M = J.M;
+    const int M = GEN ? J.M : 1;
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);      // SWIZZLE_128B tiles need 1 KB alignment
     unsigned char* bimg = ring + (size_t)p.stages * p.stage_bytes;          // nst tiles of max_m KB: [step][row m][digit t][128 B]
     unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: per tile, slabs [R x sc_box]
@@ -209,6 +197,16 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             __syncwarp();
             if (lane == 0) UTRACE(62);
         }
+        else if (warp == 1 && !GEN) {
+            // L2 prefetch of the steps the ring cannot take at once (legal before the upstream kernel
+            // has finished: L2 is the point of coherence).  Only on the single-tile path: a prefetch
+            // costs the TMA unit as much as a load, and a multi-tile CTA would queue dozens of them.
+            for (int g = p.stages + lane; g < nsteps; g += 32) {
+                const int t = g / nst, it = g - t * nst;
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                             :: "l"(J.mw), "r"(it * 128), "r"(row0 + t * p.R) : "memory");
+            }
+        }
     } else if (warp < UM_LOAD_WARPS + UM_MMA_WARPS) {
         // ---- MMA issuers: warp w takes the steps g with g % 4 == w ----
         named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // B image, unit scales and gam[] are ready
@@ -221,8 +219,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             const uint32_t tSB = tmem + UM_COL_SB;
             const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             int s = me % p.stages;
+            int t = me / nst, it = me - t * nst;                       // tile and k-block of step g, kept without divisions
             for (int g = me; g < nsteps; g += UM_MMA_WARPS) {          // whole warp waits, lane 0 issues
-                const int t = g / nst, it = g - t * nst;
                 const uint32_t tsf = tmem + UM_COL_SF + (uint32_t)s * 16u;
                 // accumulator it % 4 of tile t: fixed by the k-block alone, so that the summation order of a
                 // row does not depend on which tile of the CTA it is in (or on how many tiles a CTA takes)
@@ -244,6 +242,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 }
                 __syncwarp();
                 s += UM_MMA_WARPS; while (s >= p.stages) s -= p.stages;
+                it += UM_MMA_WARPS; while (it >= nst) { it -= nst; ++t; }
             }
             if (lane == 0) tc_commit(smem_u32(&done_bar));
             __syncwarp();
@@ -264,7 +263,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         pdl_wait();
         if (t4 == 0) UTRACE(32);
         const float* x = J.x;
-        const float* x2 = J.x2;
+        const float* x2 = GEN ? J.x2 : nullptr;
         const float lim = p.limit;
         auto ldx = [&](const float4* row, const float4* row2, int i) -> float4 {
             float4 v = row[i];
@@ -297,53 +296,67 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         }
         named_sync(1, UM_WORKERS);
         // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
-        for (int m = 0; m < M; ++m) {
+        auto row_inv = [&](int m) -> float {
             float a = 0.f;
             #pragma unroll
             for (int w = 0; w < 8; ++w) a = fmaxf(a, red[m][w]);
             const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / 3.99f) : 1.f;
-            const float inv = 16384.f / gamma;
             if (t4 < UM_NB) gam[m][t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
+            return 16384.f / gamma;
+        };
+        // 16 activations of row m (group g) -> 16 words of eight e2m1 codes (nibble j = digit of weight
+        // 4^-(7-j)), then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
+        auto split_group = [&](int m, int g, float inv, bool cached) {
             const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
             const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
-            for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
-                // 16 activations -> 16 words of eight e2m1 codes (nibble j = digit of weight 4^-(7-j)),
-                // then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
-                uint32_t W[16];
+            uint32_t W[16];
+            #pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 f = cached ? xv[q4] : ldx(xr, xr2, g * 4 + q4);
+                const float v[4] = {f.x, f.y, f.z, f.w};
                 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 f = (M == 1 && g == t4) ? xv[q4] : ldx(xr, xr2, g * 4 + q4);
-                    const float v[4] = {f.x, f.y, f.z, f.w};
-                    #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int iq = __float2int_rn(v[e] * inv);
-                        uint32_t mm = (uint32_t)min(abs(iq), 65535);
-                        mm = (mm | (mm << 8)) & 0x00FF00FFu;
-                        mm = (mm | (mm << 4)) & 0x0F0F0F0Fu;
-                        mm = (mm | (mm << 2)) & 0x33333333u;                    // one base-4 digit per nibble
-                        const uint32_t b1 = (mm >> 1) & 0x11111111u, b0 = mm & 0x11111111u;
-                        uint32_t c = (mm << 1) - (b1 & b0);                        // e2m1 code of the digit: 0,2,4,5
-                        if (iq < 0) c |= (b1 | b0) << 3;                           // sign on the non-zero digits
-                        W[q4 * 4 + e] = c;
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const int iq = __float2int_rn(v[e] * inv);
+                    uint32_t mm = (uint32_t)min(abs(iq), 65535);
+                    mm = (mm | (mm << 8)) & 0x00FF00FFu;
+                    mm = (mm | (mm << 4)) & 0x0F0F0F0Fu;
+                    mm = (mm | (mm << 2)) & 0x33333333u;                    // one base-4 digit per nibble
+                    const uint32_t b1 = (mm >> 1) & 0x11111111u, b0 = mm & 0x11111111u;
+                    uint32_t c = (mm << 1) - (b1 & b0);                        // e2m1 code of the digit: 0,2,4,5
+                    if (iq < 0) c |= (b1 | b0) << 3;                           // sign on the non-zero digits
+                    W[q4 * 4 + e] = c;
                 }
+            }
+            #pragma unroll
+            for (int h = 0; h < 16; h += 8) {
                 #pragma unroll
-                for (int h = 0; h < 16; h += 8) {
-                    #pragma unroll
-                    for (int r = 0; r < 8; r += 2) { const uint32_t t = ((W[h + r] >> 4) ^ W[h + r + 1]) & 0x0F0F0F0Fu; W[h + r] ^= t << 4; W[h + r + 1] ^= t; }
-                    #pragma unroll
-                    for (int r = 0; r < 8; ++r) if (!(r & 2)) { const uint32_t t = ((W[h + r] >> 8) ^ W[h + r + 2]) & 0x00FF00FFu; W[h + r] ^= t << 8; W[h + r + 2] ^= t; }
-                    #pragma unroll
-                    for (int r = 0; r < 4; ++r) { const uint32_t t = ((W[h + r] >> 16) ^ W[h + r + 4]) & 0x0000FFFFu; W[h + r] ^= t << 16; W[h + r + 4] ^= t; }
+                for (int r = 0; r < 8; r += 2) { const uint32_t t = ((W[h + r] >> 4) ^ W[h + r + 1]) & 0x0F0F0F0Fu; W[h + r] ^= t << 4; W[h + r + 1] ^= t; }
+                #pragma unroll
+                for (int r = 0; r < 8; ++r) if (!(r & 2)) { const uint32_t t = ((W[h + r] >> 8) ^ W[h + r + 2]) & 0x00FF00FFu; W[h + r] ^= t << 8; W[h + r + 2] ^= t; }
+                #pragma unroll
+                for (int r = 0; r < 4; ++r) { const uint32_t t = ((W[h + r] >> 16) ^ W[h + r + 4]) & 0x0000FFFFu; W[h + r] ^= t << 16; W[h + r + 4] ^= t; }
+            }
+            // W[j] (j < 8): codes of digit 7-j for activations 0..7; W[8 + j]: for activations 8..15.
+            // B image: step (256 k) = g / 16, atom m (8 rows of 128 B), row t, 16-byte chunk (g % 16) / 2
+            // swizzled with the row, half g % 2
+            const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
+            unsigned char* at = bimg + ((size_t)tile * p.max_m + m) * 1024 + hf * 8;
+            #pragma unroll
+            for (int t = 0; t < UM_NB; ++t)
+                *reinterpret_cast<uint2*>(at + t * 128 + ((ch ^ t) << 4)) = make_uint2(W[7 - t], W[15 - t]);
+        };
+        if (M == 1) {
+            const float inv = row_inv(0);
+            for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, g == t4);
+        } else {
+            // two rows per trip: two independent dependency chains for the scheduler to interleave
+            for (int m = 0; m < M; m += 2) {
+                const bool two = m + 1 < M;
+                const float inv0 = row_inv(m), inv1 = two ? row_inv(m + 1) : 0.f;
+                for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
+                    split_group(m, g, inv0, false);
+                    if (two) split_group(m + 1, g, inv1, false);
                 }
-                // W[j] (j < 8): codes of digit 7-j for activations 0..7; W[8 + j]: for activations 8..15.
-                // B image: step (256 k) = g / 16, atom m (8 rows of 128 B), row t, 16-byte chunk (g % 16) / 2
-                // swizzled with the row, half g % 2
-                const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
-                unsigned char* at = bimg + ((size_t)tile * p.max_m + m) * 1024 + hf * 8;
-                #pragma unroll
-                for (int t = 0; t < UM_NB; ++t)
-                    *reinterpret_cast<uint2*>(at + t * 128 + ((ch ^ t) << 4)) = make_uint2(W[7 - t], W[15 - t]);
             }
         }
         fence_async_smem();
@@ -362,10 +375,12 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // Software-pipelined: the next step's scale bytes are read from shared memory while this
             // step's tcgen05.st is in flight.
             const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
+            int rt = grp / nst, rit = grp - rt * nst;                  // tile and k-block of the next step to read
             auto read_scales = [&](int g, uint4 (&v)[4]) {
                 // full[g] also says that the MMAs that last read this stage's scale slot are done
                 UM_WAIT(full0 + g * 8, 0, p.status, 2);
-                const int t = g / nst, it = g - t * nst;
+                const int t = rt, it = rit;
+                rit += 2; while (rit >= nst) { rit -= nst; ++rt; }
                 const unsigned char* sl = scl + (uint32_t)t * slab_bytes;
                 const int valid = J.N - (row0 + t * p.R);            // rows of this tile that exist (may exceed R)
                 #pragma unroll
@@ -523,7 +538,9 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     if (p.stage_bytes + fixed < 16384) fixed = 16384 - p.stage_bytes;
     cudaFuncAttributes fa;
     int dev = 0, optin = 0;
-    if (cudaFuncGetAttributes(&fa, k_gemv_umma) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess ||
+    const bool gen = p.table != nullptr || p.max_m != 1 || p.T != 1;
+    auto kern = gen ? k_gemv_umma<true> : k_gemv_umma<false>;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemv_umma: attributes");
     const size_t room = (size_t)optin - fa.sharedSizeBytes - 2048;    // 1 KB alignment slack + 1 KB system reserve
     if (fixed + 2 * (size_t)p.stage_bytes > room) return B200_ENOTIMPL;
@@ -542,11 +559,11 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
       p.trace = tb + (size_t)(cnt++ % 8) * 1024 * 64; g_trace_umma = tb; }
 #endif
     const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
-    static bool ready = false;
-    if (!ready) {
-        if (cudaFuncSetAttribute(k_gemv_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) != cudaSuccess)
+    static bool ready[2] = {false, false};
+    if (!ready[gen]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) != cudaSuccess)
             return launch_failed("gemv_umma: cudaFuncSetAttribute");
-        ready = true;
+        ready[gen] = true;
     }
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(tasks); lc.blockDim = dim3(UM_THREADS); lc.dynamicSmemBytes = smem; lc.stream = s;
@@ -554,7 +571,7 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at; lc.numAttrs = 1;
-    if (cudaLaunchKernelEx(&lc, k_gemv_umma, p, maps) != cudaSuccess) return launch_failed("k_gemv_umma");
+    if (cudaLaunchKernelEx(&lc, kern, p, maps) != cudaSuccess) return launch_failed("k_gemv_umma");
     return check_launch("k_gemv_umma");
 }
 

@@ -72,6 +72,15 @@ void moe_route_batch(const float* x, const MoeLayer& L, int32_t* sel, float* wts
 void moe_route(const float* x, const MoeLayer& L, int32_t* sel, float* wts, float* logits, cudaStream_t s) {
     moe_route_batch(x, L, sel, wts, logits, 1, s);
 }
+bool moe_prepare(const MoeLayer& L) {
+    b200_moe_layer l = cl(L);
+    const int rc = b200_moe_prepare(&l);
+    if (rc == B200_ENOTIMPL) return false;
+    must(rc, "moe_prepare");
+    return true;
+}
+void moe_release(const MoeLayer& L) { b200_moe_layer l = cl(L); (void)b200_moe_release(&l); }
+
 void moe_forward_batch(const float* x, const MoeLayer& L, float* y, int32_t* sel, float* wts, float* ws, int M, cudaStream_t s) {
     const b200_moe_layer l = cl(L);
     must(b200_moe_forward(x, &l, y, sel, wts, ws, M, s), "moe_forward");

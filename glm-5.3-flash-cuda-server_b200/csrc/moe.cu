@@ -15,6 +15,7 @@
 // Geometry (hidden, inter, top-k, scale, clamp) is per layer at run time.
 #include "b200_internal.h"
 #include "gemv_core.cuh"
+#include "moe_plan.cuh"
 #include <cstdio>
 
 namespace b200 {
@@ -32,14 +33,15 @@ struct MoeArgs {
 // One warp per token.  Ranking value = sigmoid(logit) + bias, gate value = sigmoid(logit);
 // among equal ranking values the lowest expert index wins, as in the reference's serial scan
 // with a strict '>' (kernels/moe.cu:146-152).
+template <int C>                                   // candidates per lane: n_expert <= 32 * C
 __global__ void __launch_bounds__(32)
 k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restrict__ logits,
-        const float* __restrict__ bias, int E, int K, float scaling, int norm_prob) {
+        const float* __restrict__ bias, int E, int K, float scaling, int norm_prob, const __grid_constant__ MoePlan plan) {
     const int tok = blockIdx.x, lane = threadIdx.x;
     logits += (size_t)tok * E; sel += (size_t)tok * K; wts += (size_t)tok * K;
-    float score[ROUTE_MAXC], choice[ROUTE_MAXC];
+    float score[C], choice[C];
     #pragma unroll
-    for (int j = 0; j < ROUTE_MAXC; ++j) {
+    for (int j = 0; j < C; ++j) {
         const int i = lane + 32 * j;
         if (i < E) {
             score[j] = 1.f / (1.f + __expf(-logits[i]));
@@ -47,10 +49,11 @@ k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restr
         } else { score[j] = 0.f; choice[j] = -3.0e38f; }
     }
     float my_w = 0.f;                              // lane k keeps the k-th gate
+    int my_e = 0;                                  // ... and the k-th expert
     for (int k = 0; k < K; ++k) {
         float bv = -1e30f, bs = 0.f; int bi = 0x7fffffff;
         #pragma unroll
-        for (int j = 0; j < ROUTE_MAXC; ++j)
+        for (int j = 0; j < C; ++j)
             if (choice[j] > bv) { bv = choice[j]; bs = score[j]; bi = lane + 32 * j; }
         #pragma unroll
         for (int o = 16; o; o >>= 1) {
@@ -61,8 +64,8 @@ k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restr
         }
         if (bi >= E) bi = 0;                       // only if fewer than K finite candidates
         #pragma unroll
-        for (int j = 0; j < ROUTE_MAXC; ++j) if (lane + 32 * j == bi) choice[j] = -1e30f;
-        if (lane == k) my_w = bs;
+        for (int j = 0; j < C; ++j) if (lane + 32 * j == bi) choice[j] = -1e30f;
+        if (lane == k) { my_w = bs; my_e = bi; }
         if (lane == 0) sel[k] = bi;
     }
     float d = 1.f;
@@ -71,6 +74,8 @@ k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restr
         for (int k = 0; k < K; ++k) d += __shfl_sync(0xffffffffu, my_w, k);
     }
     if (lane < K) wts[lane] = my_w / d * scaling;
+    // job records of the tensor-core experts for this token's pairs (prepared layers only)
+    if (plan.j1 && lane < plan.ns) moe_plan_pair(plan, tok, lane, my_e);
 }
 
 template <int MATH>
@@ -191,9 +196,9 @@ static int grid_for(Kern kern, size_t smem, int tasks, int* grid) {
 }
 
 static int experts_forward(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
-                           const float* wts, float* act, int M, cudaStream_t s, bool allow_tensor_path) {
+                           const float* wts, float* act, int M, cudaStream_t s, bool allow_tensor_path, bool planned = false) {
     if (allow_tensor_path) {                             // prepared layers, up to 8 tokens (moe_umma.cu)
-        const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s);
+        const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s, planned);
         if (rc != B200_ENOTIMPL) return rc;
     }
     MoeArgs a{};
@@ -249,14 +254,23 @@ extern "C" size_t b200_moe_workspace_bytes(const b200_moe_layer* L, int M) {
     return align_up((size_t)M * L->n_expert * 4, 256) + scratch;
 }
 
-extern "C" int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts,
-                              float* logits, int M, b200_stream stream) {
+static int route_launch(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts, float* logits, int M,
+                        cudaStream_t stream, const MoePlan& plan) {
     if (int rc = check_layer(L, M)) return rc;
     if (!x || !sel || !wts || !logits || !L->router_bias) return B200_EINVAL;
     if (int rc = b200_nvfp4_gemm(logits, &L->router_w, x, M, L->n_expert, L->hidden, B200_BF16, stream)) return rc;
-    k_route<<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk,
-                                  L->routed_scale, L->norm_topk);
+    if (L->n_expert <= 128)
+        k_route<4><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
+    else if (L->n_expert <= 256)
+        k_route<8><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
+    else
+        k_route<ROUTE_MAXC><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
     return check_launch("k_route");
+}
+
+extern "C" int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* sel, float* wts,
+                              float* logits, int M, b200_stream stream) {
+    return route_launch(x, L, sel, wts, logits, M, stream, MoePlan{});
 }
 
 extern "C" int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
@@ -274,8 +288,14 @@ extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* 
     if (!x || !y || !sel || !wts || !ws) return B200_EINVAL;
     if ((uintptr_t)ws & 15) return B200_EALIGN;
     float* logits = static_cast<float*>(ws);
-    if (int rc = b200_moe_route(x, L, sel, wts, logits, M, stream)) return rc;
-    return b200_moe_experts(x, L, y, sel, wts, ws, M, stream);
+    float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));
+    // On a prepared layer the router kernel also writes the job records of the tensor-core experts.
+    MoePlan plan{};
+    int R_gu = 0, R_d = 0;
+    const bool planned = moe_umma_plan_args(x, L, act, M, &plan, &R_gu, &R_d) == B200_OK;
+    if (!planned) plan = MoePlan{};
+    if (int rc = route_launch(x, L, sel, wts, logits, M, stream, plan)) return rc;
+    return experts_forward(x, L, y, sel, wts, act, M, stream, true, planned);
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------

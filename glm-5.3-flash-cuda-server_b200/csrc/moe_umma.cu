@@ -14,6 +14,7 @@
 // are read once from HBM and then from L2): a token's result does not depend on what else is
 // in the batch, bit for bit.  The gate-weighted sum runs over the slots in slot order.
 #include "b200_internal.h"
+#include "moe_plan.cuh"
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -55,28 +56,11 @@ static int pick_rows(int n_jobs, int N) {
     return best;
 }
 
-__global__ void k_moe_plan(UmJob* __restrict__ j1, UmJob* __restrict__ j2, const int32_t* __restrict__ sel,
-                           const b200_nvfp4_mat* __restrict__ experts, const b200_nvfp4_mat* __restrict__ shared,
-                           const unsigned char* __restrict__ maps, const float* __restrict__ x,
-                           float* __restrict__ gbuf, float* __restrict__ ubuf, float* __restrict__ part,
-                           int M, int topk, int ns, int E, int H, int I) {
+__global__ void k_moe_plan(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int M) {
     const int pair = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pair >= M * ns) return;
-    const int m = pair / ns, slot = pair - m * ns;
-    int e = E;                                        // the shared expert's maps come last
-    const b200_nvfp4_mat* mats = shared;
-    if (slot < topk) {
-        e = sel[(size_t)m * topk + slot];
-        e = e < 0 ? 0 : (e >= E ? E - 1 : e);
-        mats = experts + (size_t)e * 3;
-    }
-    const unsigned char* mp = maps + (size_t)e * 6 * 128;
-    const float* xm = x + (size_t)m * H;
-    float* g = gbuf + (size_t)pair * I;
-    float* u = ubuf + (size_t)pair * I;
-    j1[2 * pair] = UmJob{g, xm, nullptr, mats[0].gscale, mp, mp + 128, I, 1, 0, 0};
-    j1[2 * pair + 1] = UmJob{u, xm, nullptr, mats[1].gscale, mp + 256, mp + 384, I, 1, 0, 0};
-    j2[pair] = UmJob{part + (size_t)pair * H, g, u, mats[2].gscale, mp + 512, mp + 640, H, 1, 0, 0};
+    if (pair >= M * q.ns) return;
+    const int m = pair / q.ns, slot = pair - m * q.ns;
+    moe_plan_pair(q, m, slot, slot < q.topk ? sel[(size_t)m * q.topk + slot] : 0);
 }
 
 // y[m, h] = sum over the routed slots in slot order of wts[m, k] * part[m, k, h], plus the shared expert's row.
@@ -108,28 +92,41 @@ size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
     return up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4);
 }
 
-// B200_ENOTIMPL: not prepared, too many tokens, or a shape the kernel does not take -> the caller
-// runs the CUDA-core experts.
-int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
-                     void* scratch, int M, cudaStream_t s) {
+// Fills `q` for a call on a prepared layer.  B200_ENOTIMPL: not prepared, too many tokens, or an
+// unaligned activation -> the caller runs the CUDA-core experts.
+int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, int M, MoePlan* q, int* R_gu, int* R_d) {
     if (M > MU_MAX_TOKENS || ((uintptr_t)x & 15)) return B200_ENOTIMPL;
     const Prepared* P = find_prepared(L);
     if (!P) return B200_ENOTIMPL;
     const int ns = L->topk + (L->shared ? 1 : 0), pairs = M * ns, H = L->hidden, I = L->inter;
     char* w = static_cast<char*>(scratch);
-    UmJob* j1 = reinterpret_cast<UmJob*>(w);
-    UmJob* j2 = j1 + (size_t)2 * pairs;
+    q->j1 = reinterpret_cast<UmJob*>(w);
+    q->j2 = q->j1 + (size_t)2 * pairs;
     w += up256((size_t)M * (L->topk + 1) * 3 * sizeof(UmJob));
-    float* gbuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
-    float* ubuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
-    float* part = reinterpret_cast<float*>(w);
-    k_moe_plan<<<(pairs + 127) / 128, 128, 0, s>>>(j1, j2, sel, L->experts, L->shared, P->maps, x, gbuf, ubuf, part,
-                                                   M, L->topk, ns, L->n_expert, H, I);
-    if (int rc = check_launch("k_moe_plan")) return rc;
-    if (int rc = umma_table_launch(j1, 2 * pairs, I, H, P->R_gu, 0.f, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
-    if (int rc = umma_table_launch(j2, pairs, H, I, P->R_d, L->swiglu_limit, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
-    const int n4 = M * (H >> 2);
-    k_moe_combine<<<(n4 + 255) / 256, 256, 0, s>>>(y, part, wts, M, L->topk, ns, H);
+    q->gbuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
+    q->ubuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
+    q->part = reinterpret_cast<float*>(w);
+    q->experts = L->experts; q->shared = L->shared; q->maps = P->maps; q->x = x;
+    q->topk = L->topk; q->ns = ns; q->E = L->n_expert; q->H = H; q->I = I;
+    *R_gu = P->R_gu; *R_d = P->R_d;
+    return B200_OK;
+}
+
+// The experts of a planned call.  planned: the job tables were already written (by the router).
+int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                     void* scratch, int M, cudaStream_t s, bool planned) {
+    MoePlan q{};
+    int R_gu = 0, R_d = 0;
+    if (int rc = moe_umma_plan_args(x, L, scratch, M, &q, &R_gu, &R_d)) return rc;
+    const int pairs = M * q.ns;
+    if (!planned) {
+        k_moe_plan<<<(pairs + 127) / 128, 128, 0, s>>>(q, sel, M);
+        if (int rc = check_launch("k_moe_plan")) return rc;
+    }
+    if (int rc = umma_table_launch(q.j1, 2 * pairs, q.I, q.H, R_gu, 0.f, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_table_launch(q.j2, pairs, q.H, q.I, R_d, L->swiglu_limit, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    const int n4 = M * (q.H >> 2);
+    k_moe_combine<<<(n4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, M, q.topk, q.ns, q.H);
     return check_launch("k_moe_combine");
 }
 

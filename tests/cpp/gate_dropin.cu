@@ -130,6 +130,21 @@ int main() {
         const bool ok = memcmp(a.data(), b.data(), a.size() * 4) == 0 && nz > (int)a.size() / 2;
         printf("moe_forward_batch rows == moe_forward  %s\n", ok ? "PASS bit-identical" : "FAIL");
         fails += !ok;
+        // the same after moe_prepare (tensor-core experts): still row == single call bit for bit, and
+        // close to the CUDA-core result
+        if (moe_prepare(L)) {
+            moe_forward_batch(dx, L, y, sel, wts, ws, M, 0);
+            for (int m = 0; m < M; ++m) moe_forward(dx + (size_t)m * H, L, y1 + (size_t)m * H, sel, wts, ws, 0);
+            CU(cudaDeviceSynchronize());
+            std::vector<float> c((size_t)M * H), d((size_t)M * H);
+            CU(cudaMemcpy(c.data(), y, c.size() * 4, cudaMemcpyDeviceToHost)); CU(cudaMemcpy(d.data(), y1, d.size() * 4, cudaMemcpyDeviceToHost));
+            double num = 0, den = 0;
+            for (size_t i = 0; i < c.size(); ++i) { num += (double)(c[i] - a[i]) * (c[i] - a[i]); den += (double)a[i] * a[i]; }
+            const bool ok2 = memcmp(c.data(), d.data(), c.size() * 4) == 0 && memcmp(c.data(), a.data(), c.size() * 4) != 0 && num <= 1e-6 * den;
+            printf("prepared layer: rows == single calls, rel-L2 to CUDA-core %.2e  %s\n", sqrt(num / (den + 1e-30)), ok2 ? "PASS" : "FAIL");
+            fails += !ok2;
+            moe_release(L);
+        } else { printf("moe_prepare refused the gate's geometry  FAIL\n"); fails++; }
     }
     unsigned st = 0; b200_nvfp4_device_status(&st, 0);
     if (st) { printf("device status %08x\n", st); fails++; }
