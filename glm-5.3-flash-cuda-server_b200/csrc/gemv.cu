@@ -171,6 +171,46 @@ k_gemm_dense(float* __restrict__ y, const void* __restrict__ W, const float* __r
     }
 }
 
+// The same product for few output rows (the MoE router: 144 x 4096): one CTA per row, the row's K
+// split over 256 threads so that every weight load of the kernel is in flight at once, then a
+// fixed-order reduction (lanes by shuffle, the eight warps in warp order).  bf16 weights, 16-byte
+// aligned rows.
+template <int M>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_gemm_dense_row(float* __restrict__ y, const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, int N, int K) {
+    __shared__ float part[GEMV_WARPS][M];
+    const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4* Wr = reinterpret_cast<const uint4*>(W + (size_t)n * K);
+    float acc[M];
+    #pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    for (int i = threadIdx.x; i < (K >> 3); i += GEMV_THREADS) {
+        const uint4 raw = Wr[i];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float wf[8];
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
+        #pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float* xr = x + (size_t)m * K + (size_t)i * 8;
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) acc[m] = fmaf(wf[j], xr[j], acc[m]);
+        }
+    }
+    #pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) part[warp][m] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < M) {
+        float v = 0.f;
+        #pragma unroll
+        for (int w = 0; w < GEMV_WARPS; ++w) v += part[w][threadIdx.x];
+        y[(size_t)threadIdx.x * N + n] = v;
+    }
+}
+
 __global__ void k_f32_to_bf16(__nv_bfloat16* d, const float* s, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) d[i] = __float2bfloat16(s[i]);
@@ -286,6 +326,10 @@ static int launch_dense(float* y, const void* W, const float* x, int N, int K, i
     const int grid = (N + GEMV_WARPS - 1) / GEMV_WARPS;
     const int eb = dtype == B200_F32 ? 4 : 2;
     const bool vec = (((uintptr_t)W & 15) == 0) && ((((size_t)K * eb) & 15) == 0);
+    if (dtype == B200_BF16 && vec && N <= 2048 && K >= 2048) {       // few rows: latency-bound, one CTA per row
+        k_gemm_dense_row<M><<<N, GEMV_THREADS, 0, s>>>(y, static_cast<const __nv_bfloat16*>(W), x, N, K);
+        return check_launch("k_gemm_dense_row");
+    }
     if (dtype == B200_F32) {
         if (vec) k_gemm_dense<M, false, true><<<grid, GEMV_THREADS, 0, s>>>(y, W, x, N, K);
         else     k_gemm_dense<M, false, false><<<grid, GEMV_THREADS, 0, s>>>(y, W, x, N, K);
