@@ -32,7 +32,8 @@ UMMA = os.environ.get('B200_NVFP4_UMMA') != '0'          # the library's default
 if UMMA:
     DTYPE = 'nvfp4 weights (e2m1 + e4m3 block scales) x activations as eight e2m1 digit columns (14 fractional bits of the row maximum), fp32 accumulate'
     MATH = 'tcgen05.mma kind::mxf4nvf4.block_scale.block16, accumulators in TMEM'
-    KERNEL = 'k_gemv_umma'
+    KERNEL = 'k_gemv_umma<0>'
+    TRAFFIC = 29780480         # dram read + write bytes per launch, ncu capture of this command (summary under profiles/)
 else:
     DTYPE = 'nvfp4 weights (e2m1 + e4m3 scales), f16 products, f32 accumulate'
     MATH = 'fp32-mac' if os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'
@@ -453,7 +454,7 @@ def main():
                    'launch': 'steps captured back to back in CUDA graphs; programmatic dependent launch; weights declared stable',
                    'math': MATH},
         'roofline': {'bound': 'hbm', 'kernel': KERNEL, 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
-                     'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': None,
+                     'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': TRAFFIC if UMMA else None,
                      'algorithmic_bytes_per_launch': nbytes},
         'e2e': {'value': nbytes / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
