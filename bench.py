@@ -321,6 +321,7 @@ def bench_ep(P, a, rank, local, world, peak):
     if rank == 0:
         full = [P.ep_gpu.expert_weights(50, 0, e, H, I, dev) for e in range(E + 1)]
         ref_layer = P.MoeLayer(layers[0].router, layers[0].bias, full[:E], full[E], topk, H, I)
+        if layers[0].tensor_core: P.moe_prepare(ref_layer)
         y_ref, sel_ref, _ = P.moe_forward(ref_layer, x0)
         par = {'rel_l2': ((y_ep - y_ref).norm() / y_ref.norm()).item(), 'sel_equal': bool(torch.equal(sel_ep, sel_ref))}
     stats = [L.ep.last_stats for L in layers]
@@ -331,12 +332,12 @@ def bench_ep(P, a, rank, local, world, peak):
     print(json.dumps({
         'metric': 'nvfp4_moe_ep_hbm_tbps', 'value': val, 'unit': 'TB/s', 'n_gpus': world, 'steps': a.steps, 'warmup': a.warmup,
         'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
-        'dtype': 'nvfp4 weights, f16 products, f32 accumulate', 'data': 'synthetic',
+        'dtype': DTYPE, 'data': 'synthetic',
         'config': {'workload': 'expert-parallel MoE: %d tokens x 4096, 144 experts (%d per GPU), top-8 + shared expert, Zipf(1.1) routing bias, 3 stacked layers (configs[4])' % (T, E // world),
                    'l2': 'inputs larger than L2: %.1f GB of expert weights per rank' % (Lyr * (E // world + 1) * layers[0].expert_bytes / 1e9),
                    'collective': 'NCCL all_to_all_single: counts, token rows (fp32), expert ids; reverse for outputs'},
         'tokens_per_s': T / (ms * 1e-3), 'us_per_layer': ms * 1e3 / Lyr,
-        'roofline': {'bound': 'hbm', 'kernel': 'k_expert_act', 'achieved': val * 1e3 / world, 'peak': peak, 'unit': 'GB/s per GPU',
+        'roofline': {'bound': 'hbm', 'kernel': 'k_gemv_umma<1> (experts, rows grouped by expert)' if layers[0].tensor_core else 'k_expert_act', 'achieved': val * 1e3 / world, 'peak': peak, 'unit': 'GB/s per GPU',
                      'frac': val * 1e3 / world / peak, 'traffic': None},
         'e2e': {'value': total_b / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': Tl * H * 4 * world, 'd2h_bytes_per_step': Tl * H * 4 * world},

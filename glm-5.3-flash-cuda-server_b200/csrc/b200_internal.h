@@ -43,7 +43,13 @@ int nvfp4_multi_umma(const GemvParams& p, int M, cudaStream_t s);
 // clamped SwiGLU of two vectors, x = silu(min(x, limit)) * clamp(x2, -limit, limit) (the MoE down
 // projection reads the gate and up products directly).  mw, ms: CUtensorMap of packed weights and
 // of scales in GLOBAL memory (job-table launches); nullptr = the maps passed as kernel parameters.
-struct UmJob { float* y; const float* x; const float* x2; const float* gs; const void* mw; const void* ms; int N; int M; int task0; int pad; };
+// bimg != nullptr: the activation rows were already split into their B image (K/256 x 8 KB, rows at a
+// stride of 8) and digit weights gam[M*8] by k_split_rows; x and x2 are then not read.
+struct UmJob { float* y; const float* x; const float* x2; const float* gs; const void* mw; const void* ms;
+               const unsigned char* bimg; const float* gam; int N; int M; int task0; int pad; };
+// One unit of k_split_rows: M rows of x (SwiGLU with x2 when x2 != nullptr) -> bimg, gam.  M = 0: nothing.
+struct SplitJob { const float* x; const float* x2; unsigned char* bimg; float* gam; int M; int pad; };
+int umma_split_launch(const SplitJob* jobs, int n_jobs, int K, float limit, cudaStream_t s);
 bool umma_shape_ok(int K);
 // moe_umma.cu: the experts of a prepared layer on the tensor-core kernel; B200_ENOTIMPL = not applicable.
 size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M);
@@ -52,6 +58,6 @@ int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, i
 int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
                      void* scratch, int M, cudaStream_t s, bool planned);
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
-int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, cudaStream_t s);
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s);
 
 }  // namespace b200

@@ -101,13 +101,117 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
+// Splits M activation rows x[M, K] (the clamped SwiGLU of x and x2 when x2 != nullptr) into the B image
+// `bimg` ([K/256 steps][stride_m rows][8 digits][128 B], 128B-swizzled; shared or global memory) and
+// writes gam[m*8 + t] = gamma_m 4^-t.  256 threads (t4 = 0..255) call it together; `red` is shared
+// scratch [UM_MAX_M][8]; named barrier 1 is used among the 256.
+template <bool SINGLE>
+__device__ __forceinline__ void split_rows(const float* x, const float* x2, float lim, int M, int K, int stride_m,
+                                           unsigned char* bimg, float* gam, float (*red)[8], int t4) {
+    const int lane = t4 & 31;
+    auto ldx = [&](const float4* row, const float4* row2, int i) -> float4 {
+        float4 v = row[i];
+        if (row2) {
+            const float4 u = row2[i];
+            const float g[4] = {fminf(v.x, lim), fminf(v.y, lim), fminf(v.z, lim), fminf(v.w, lim)};
+            const float w[4] = {fminf(fmaxf(u.x, -lim), lim), fminf(fmaxf(u.y, -lim), lim), fminf(fmaxf(u.z, -lim), lim), fminf(fmaxf(u.w, -lim), lim)};
+            v = make_float4((g[0] / (1.f + __expf(-g[0]))) * w[0], (g[1] / (1.f + __expf(-g[1]))) * w[1],
+                            (g[2] / (1.f + __expf(-g[2]))) * w[2], (g[3] / (1.f + __expf(-g[3]))) * w[3]);
+        }
+        return v;
+    };
+    // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
+    // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
+    float4 xv[4];
+    for (int m = 0; m < M; ++m) {
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+        const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
+        float a = 0.f;
+        for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 v = ldx(xr, xr2, i + q);
+                if (SINGLE && i == t4 * 4) xv[q] = v;
+                a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+        }
+        a = warp_max(a);
+        if (lane == 0) red[m][t4 >> 5] = a;
+    }
+    named_sync(1, UM_WORKERS);
+    // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
+    auto row_inv = [&](int m) -> float {
+        float a = 0.f;
+        #pragma unroll
+        for (int w = 0; w < 8; ++w) a = fmaxf(a, red[m][w]);
+        const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / 3.99f) : 1.f;
+        if (t4 < UM_NB) gam[m * UM_NB + t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
+        return 16384.f / gamma;
+    };
+    // 16 activations of row m (group g) -> 16 words of eight e2m1 codes (nibble j = digit of weight
+    // 4^-(7-j)), then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
+    auto split_group = [&](int m, int g, float inv, bool cached) {
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+        const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
+        uint32_t W[16];
+        #pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const float4 f = cached ? xv[q4] : ldx(xr, xr2, g * 4 + q4);
+            const float v[4] = {f.x, f.y, f.z, f.w};
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int iq = __float2int_rn(v[e] * inv);
+                uint32_t mm = (uint32_t)min(abs(iq), 65535);
+                mm = (mm | (mm << 8)) & 0x00FF00FFu;
+                mm = (mm | (mm << 4)) & 0x0F0F0F0Fu;
+                mm = (mm | (mm << 2)) & 0x33333333u;                    // one base-4 digit per nibble
+                const uint32_t b1 = (mm >> 1) & 0x11111111u, b0 = mm & 0x11111111u;
+                uint32_t c = (mm << 1) - (b1 & b0);                        // e2m1 code of the digit: 0,2,4,5
+                if (iq < 0) c |= (b1 | b0) << 3;                           // sign on the non-zero digits
+                W[q4 * 4 + e] = c;
+            }
+        }
+        #pragma unroll
+        for (int h = 0; h < 16; h += 8) {
+            #pragma unroll
+            for (int r = 0; r < 8; r += 2) { const uint32_t t = ((W[h + r] >> 4) ^ W[h + r + 1]) & 0x0F0F0F0Fu; W[h + r] ^= t << 4; W[h + r + 1] ^= t; }
+            #pragma unroll
+            for (int r = 0; r < 8; ++r) if (!(r & 2)) { const uint32_t t = ((W[h + r] >> 8) ^ W[h + r + 2]) & 0x00FF00FFu; W[h + r] ^= t << 8; W[h + r + 2] ^= t; }
+            #pragma unroll
+            for (int r = 0; r < 4; ++r) { const uint32_t t = ((W[h + r] >> 16) ^ W[h + r + 4]) & 0x0000FFFFu; W[h + r] ^= t << 16; W[h + r + 4] ^= t; }
+        }
+        // W[j] (j < 8): codes of digit 7-j for activations 0..7; W[8 + j]: for activations 8..15.
+        // B image: step (256 k) = g / 16, atom m (8 rows of 128 B), row t, 16-byte chunk (g % 16) / 2
+        // swizzled with the row, half g % 2
+        const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
+        unsigned char* at = bimg + ((size_t)tile * stride_m + m) * 1024 + hf * 8;
+        #pragma unroll
+        for (int t = 0; t < UM_NB; ++t)
+            *reinterpret_cast<uint2*>(at + t * 128 + ((ch ^ t) << 4)) = make_uint2(W[7 - t], W[15 - t]);
+    };
+    if (SINGLE || M == 1) {
+        const float inv = row_inv(0);
+        for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, SINGLE && g == t4);
+    } else {
+        // two rows per trip: two independent dependency chains for the scheduler to interleave
+        for (int m = 0; m < M; m += 2) {
+            const bool two = m + 1 < M;
+            const float inv0 = row_inv(m), inv1 = two ? row_inv(m + 1) : 0.f;
+            for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
+                split_group(m, g, inv0, false);
+                if (two) split_group(m + 1, g, inv1, false);
+            }
+        }
+    }
+}
+
 // GEN = false: the decode hot path (one activation row, one tile per CTA, jobs in the parameters,
 // plain activations) with the general loops folded away at compile time.
 template <bool GEN>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar;
+    __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar, bi_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ float gam[UM_MAX_M][UM_NB], red[UM_MAX_M][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -121,6 +225,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         const int per_job = p.tiles_per_job / T;     // CTAs per job (the host makes T divide tiles_per_job)
         ji = (int)blockIdx.x / per_job;
         J = p.table[ji];
+        if (J.N <= 0) return;                        // an unused slot of the table: the whole CTA leaves
         J.task0 = ji * per_job;
     } else {
         #pragma unroll
@@ -144,6 +249,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         else if (i >= 128 && i < 128 + nsteps) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
         else if (i == 192) mbar_init(smem_u32(&done_bar), UM_MMA_WARPS);
         else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
+        else if (i == 194) mbar_init(smem_u32(&bi_bar), 1);
         mbar_fence_init();
     }
     if (warp == UM_LOAD_WARPS) {
@@ -262,102 +368,17 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         const float gsv = J.gs[0];                       // weight data: with stable weights it may be read early
         pdl_wait();
         if (t4 == 0) UTRACE(32);
-        const float* x = J.x;
-        const float* x2 = GEN ? J.x2 : nullptr;
-        const float lim = p.limit;
-        auto ldx = [&](const float4* row, const float4* row2, int i) -> float4 {
-            float4 v = row[i];
-            if (row2) {
-                const float4 u = row2[i];
-                const float g[4] = {fminf(v.x, lim), fminf(v.y, lim), fminf(v.z, lim), fminf(v.w, lim)};
-                const float w[4] = {fminf(fmaxf(u.x, -lim), lim), fminf(fmaxf(u.y, -lim), lim), fminf(fmaxf(u.z, -lim), lim), fminf(fmaxf(u.w, -lim), lim)};
-                v = make_float4((g[0] / (1.f + __expf(-g[0]))) * w[0], (g[1] / (1.f + __expf(-g[1]))) * w[1],
-                                (g[2] / (1.f + __expf(-g[2]))) * w[2], (g[3] / (1.f + __expf(-g[3]))) * w[3]);
-            }
-            return v;
-        };
-        // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
-        // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
-        float4 xv[4];
-        for (int m = 0; m < M; ++m) {
-            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
-            const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
-            float a = 0.f;
-            for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
-                #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 v = ldx(xr, xr2, i + q);
-                    if (i == t4 * 4) xv[q] = v;
-                    a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-            }
-            a = warp_max(a);
-            if (lane == 0) red[m][warp - UM_LOAD_WARPS - UM_MMA_WARPS] = a;
-        }
-        named_sync(1, UM_WORKERS);
-        // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
-        auto row_inv = [&](int m) -> float {
-            float a = 0.f;
-            #pragma unroll
-            for (int w = 0; w < 8; ++w) a = fmaxf(a, red[m][w]);
-            const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / 3.99f) : 1.f;
-            if (t4 < UM_NB) gam[m][t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
-            return 16384.f / gamma;
-        };
-        // 16 activations of row m (group g) -> 16 words of eight e2m1 codes (nibble j = digit of weight
-        // 4^-(7-j)), then two 8x8 nibble transposes so that each digit's 16 codes are contiguous.
-        auto split_group = [&](int m, int g, float inv, bool cached) {
-            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
-            const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
-            uint32_t W[16];
-            #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                const float4 f = cached ? xv[q4] : ldx(xr, xr2, g * 4 + q4);
-                const float v[4] = {f.x, f.y, f.z, f.w};
-                #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int iq = __float2int_rn(v[e] * inv);
-                    uint32_t mm = (uint32_t)min(abs(iq), 65535);
-                    mm = (mm | (mm << 8)) & 0x00FF00FFu;
-                    mm = (mm | (mm << 4)) & 0x0F0F0F0Fu;
-                    mm = (mm | (mm << 2)) & 0x33333333u;                    // one base-4 digit per nibble
-                    const uint32_t b1 = (mm >> 1) & 0x11111111u, b0 = mm & 0x11111111u;
-                    uint32_t c = (mm << 1) - (b1 & b0);                        // e2m1 code of the digit: 0,2,4,5
-                    if (iq < 0) c |= (b1 | b0) << 3;                           // sign on the non-zero digits
-                    W[q4 * 4 + e] = c;
-                }
-            }
-            #pragma unroll
-            for (int h = 0; h < 16; h += 8) {
-                #pragma unroll
-                for (int r = 0; r < 8; r += 2) { const uint32_t t = ((W[h + r] >> 4) ^ W[h + r + 1]) & 0x0F0F0F0Fu; W[h + r] ^= t << 4; W[h + r + 1] ^= t; }
-                #pragma unroll
-                for (int r = 0; r < 8; ++r) if (!(r & 2)) { const uint32_t t = ((W[h + r] >> 8) ^ W[h + r + 2]) & 0x00FF00FFu; W[h + r] ^= t << 8; W[h + r + 2] ^= t; }
-                #pragma unroll
-                for (int r = 0; r < 4; ++r) { const uint32_t t = ((W[h + r] >> 16) ^ W[h + r + 4]) & 0x0000FFFFu; W[h + r] ^= t << 16; W[h + r + 4] ^= t; }
-            }
-            // W[j] (j < 8): codes of digit 7-j for activations 0..7; W[8 + j]: for activations 8..15.
-            // B image: step (256 k) = g / 16, atom m (8 rows of 128 B), row t, 16-byte chunk (g % 16) / 2
-            // swizzled with the row, half g % 2
-            const int tile = g >> 4, ch = (g & 15) >> 1, hf = g & 1;
-            unsigned char* at = bimg + ((size_t)tile * p.max_m + m) * 1024 + hf * 8;
-            #pragma unroll
-            for (int t = 0; t < UM_NB; ++t)
-                *reinterpret_cast<uint2*>(at + t * 128 + ((ch ^ t) << 4)) = make_uint2(W[7 - t], W[15 - t]);
-        };
-        if (M == 1) {
-            const float inv = row_inv(0);
-            for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, g == t4);
+        if (GEN && J.bimg) {
+            // The B image was split once for all CTAs of the job by k_split_rows: copy it in.
+            const uint32_t total = (uint32_t)nst * (uint32_t)p.max_m * 1024u;
+            if (t4 == 0) mbar_expect_tx(smem_u32(&bi_bar), total);
+            named_sync(1, UM_WORKERS);
+            for (uint32_t o = (uint32_t)t4 * 16384u; o < total; o += UM_WORKERS * 16384u)
+                bulk_g2s(smem_u32(bimg) + o, J.bimg + o, min(16384u, total - o), smem_u32(&bi_bar));
+            if (t4 < M * UM_NB) (&gam[0][0])[t4] = J.gam[t4];
+            UM_WAIT(smem_u32(&bi_bar), 0, p.status, 7);
         } else {
-            // two rows per trip: two independent dependency chains for the scheduler to interleave
-            for (int m = 0; m < M; m += 2) {
-                const bool two = m + 1 < M;
-                const float inv0 = row_inv(m), inv1 = two ? row_inv(m + 1) : 0.f;
-                for (int g = t4; g < (K >> 4); g += UM_WORKERS) {
-                    split_group(m, g, inv0, false);
-                    if (two) split_group(m + 1, g, inv1, false);
-                }
-            }
+            split_rows<!GEN>(J.x, GEN ? J.x2 : nullptr, p.limit, M, K, p.max_m, bimg, &gam[0][0], red, t4);
         }
         fence_async_smem();
         tc_fence_before();
@@ -517,7 +538,7 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
-        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr, g.j[i].N, M, tasks, 0};
+        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr, nullptr, nullptr, g.j[i].N, M, tasks, 0};
         tasks += (g.j[i].N + R - 1) / R;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
@@ -581,6 +602,21 @@ static bool scale_box(int K, int* box, int* swz) {
     return false;
 }
 
+// ---- activation rows split once for many CTAs ------------------------------------------------------
+__global__ void __launch_bounds__(UM_WORKERS)
+k_split_rows(const SplitJob* __restrict__ jobs, int K, float limit) {
+    __shared__ float red[UM_MAX_M][8];
+    pdl_wait();
+    const SplitJob j = jobs[blockIdx.x];
+    if (j.M <= 0) return;
+    split_rows<false>(j.x, j.x2, limit, j.M, K, UM_MAX_M, j.bimg, j.gam, red, (int)threadIdx.x);
+}
+
+int umma_split_launch(const SplitJob* jobs, int n_jobs, int K, float limit, cudaStream_t s) {
+    k_split_rows<<<n_jobs, UM_WORKERS, 0, s>>>(jobs, K, limit);
+    return check_launch("k_split_rows");
+}
+
 // ---- job-table launches (the MoE experts) ---------------------------------------------------------
 bool umma_shape_ok(int K) { int b, z; return !(K & 255) && K <= 16384 && scale_box(K, &b, &z) && encode_fn(); }
 
@@ -592,12 +628,12 @@ int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int
     return B200_OK;
 }
 
-// n_jobs single-row jobs of N rows each, described by `table` (device memory, filled by an earlier
+// n_jobs jobs of N weight rows and up to max_m activation rows each, described by `table` (device memory, filled by an earlier
 // kernel of the stream); every job's tensor maps were encoded with box height R.
-int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, cudaStream_t s) {
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s) {
     static UmMaps none{};                            // unused in table mode, still a kernel parameter
     UmParams p{};
-    p.table = table; p.limit = limit; p.n_jobs = n_jobs; p.K = K; p.R = R; p.max_m = 1;
+    p.table = table; p.limit = limit; p.n_jobs = n_jobs; p.K = K; p.R = R; p.max_m = max_m;
     p.tiles_per_job = (N + R - 1) / R;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     // Tiles per CTA: as many as still leave every SM a CTA.  A CTA splits its activation row and
@@ -605,7 +641,7 @@ int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float
     // (accumulator columns), and the tiles' scale rows must fit beside four stages.
     const int nst = K / 256, nsm = sm_count();
     p.T = 1;
-    for (int T = 2; T <= 8; ++T) {
+    for (int T = 2; T * max_m <= 8; ++T) {
         if (p.tiles_per_job % T || T * nst > UM_MAX_STEPS) continue;
         if ((size_t)T * R * (K / 16) + (size_t)nst * 1024 + 4 * (((size_t)R * 128 + 1023) & ~(size_t)1023) > 200 * 1024) continue;
         if ((long)n_jobs * (p.tiles_per_job / T) >= nsm - nsm / 16) p.T = T;

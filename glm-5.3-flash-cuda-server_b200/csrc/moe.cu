@@ -250,7 +250,7 @@ static size_t legacy_workspace_bytes(const b200_moe_layer* L, int M) {
 extern "C" size_t b200_moe_workspace_bytes(const b200_moe_layer* L, int M) {
     if (!L || M < 1) return 0;
     size_t scratch = align_up((size_t)M * (L->topk + 1) * L->inter * 4, 256);
-    if (M <= 8) scratch = std::max(scratch, moe_umma_ws_bytes(L, M));
+    scratch = std::max(scratch, moe_umma_ws_bytes(L, M));
     return align_up((size_t)M * L->n_expert * 4, 256) + scratch;
 }
 

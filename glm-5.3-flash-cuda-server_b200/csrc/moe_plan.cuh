@@ -24,9 +24,9 @@ __device__ __forceinline__ void moe_plan_pair(const MoePlan& q, int m, int slot,
     const float* xm = q.x + (size_t)m * q.H;
     float* g = q.gbuf + (size_t)pair * q.I;
     float* u = q.ubuf + (size_t)pair * q.I;
-    q.j1[2 * pair] = UmJob{g, xm, nullptr, mats[0].gscale, mp, mp + 128, q.I, 1, 0, 0};
-    q.j1[2 * pair + 1] = UmJob{u, xm, nullptr, mats[1].gscale, mp + 256, mp + 384, q.I, 1, 0, 0};
-    q.j2[pair] = UmJob{q.part + (size_t)pair * q.H, g, u, mats[2].gscale, mp + 512, mp + 640, q.H, 1, 0, 0};
+    q.j1[2 * pair] = UmJob{g, xm, nullptr, mats[0].gscale, mp, mp + 128, nullptr, nullptr, q.I, 1, 0, 0};
+    q.j1[2 * pair + 1] = UmJob{u, xm, nullptr, mats[1].gscale, mp + 256, mp + 384, nullptr, nullptr, q.I, 1, 0, 0};
+    q.j2[pair] = UmJob{q.part + (size_t)pair * q.H, g, u, mats[2].gscale, mp + 512, mp + 640, nullptr, nullptr, q.H, 1, 0, 0};
 }
 
 }  // namespace b200

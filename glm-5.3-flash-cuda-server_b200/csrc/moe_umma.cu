@@ -63,33 +63,117 @@ __global__ void k_moe_plan(const __grid_constant__ MoePlan q, const int32_t* __r
     moe_plan_pair(q, m, slot, slot < q.topk ? sel[(size_t)m * q.topk + slot] : 0);
 }
 
-// y[m, h] = sum over the routed slots in slot order of wts[m, k] * part[m, k, h], plus the shared expert's row.
+// y[m, h] = sum over the routed slots in slot order of wts[m, k] * part[row(m, k), h], plus the shared expert's
+// row.  row(m, k) = m * ns + k, or posof[m * ns + k] when the rows were grouped by expert.
 __global__ void k_moe_combine(float* __restrict__ y, const float* __restrict__ part, const float* __restrict__ wts,
-                              int M, int topk, int ns, int H) {
+                              const int* __restrict__ posof, int M, int topk, int ns, int H) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;          // float4 index
     const int per = H >> 2;
     if (i >= M * per) return;
     const int m = i / per, h4 = i - m * per;
-    const float4* p = reinterpret_cast<const float4*>(part + (size_t)m * ns * H) + h4;
+    const float4* p = reinterpret_cast<const float4*>(part) + h4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < topk; ++k) {
         const float w = wts[(size_t)m * topk + k];
-        const float4 v = p[(size_t)k * per];
+        const int row = posof ? posof[m * ns + k] : m * ns + k;
+        const float4 v = p[(size_t)row * per];
         acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
     }
     if (ns > topk) {
-        const float4 v = p[(size_t)topk * per];
+        const int row = posof ? posof[m * ns + topk] : m * ns + topk;
+        const float4 v = p[(size_t)row * per];
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     reinterpret_cast<float4*>(y)[i] = acc;
 }
 
+// ---- more than 8 tokens: rows grouped by expert ---------------------------------------------------
+// One CTA sorts the (token, slot) pairs by expert (counting sort; the order inside an expert's
+// group is whatever the atomics give, which is harmless: every row is computed on its own) and
+// writes one job per expert and chunk of up to 8 rows, so that an expert's weights are read once
+// per 8 rows that chose it.  Job slots beyond the ones needed get N = 0 and their CTAs return at once.
+constexpr int MG_MAX_GROUPS = 513;                   // n_expert <= 512, plus the shared expert
+
+__global__ void __launch_bounds__(1024)
+k_moe_group(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int* __restrict__ posof,
+            const float* __restrict__ xg, SplitJob* __restrict__ s1, SplitJob* __restrict__ s2,
+            unsigned char* __restrict__ img1, unsigned char* __restrict__ img2, float* __restrict__ gam1,
+            float* __restrict__ gam2, int M, int max_jobs) {
+    __shared__ int cnt[MG_MAX_GROUPS], off[MG_MAX_GROUPS], jstart[MG_MAX_GROUPS], cursor[MG_MAX_GROUPS];
+    __shared__ int total_jobs;
+    const int G = q.E + 1, pairs = M * q.ns;
+    for (int e = threadIdx.x; e < G; e += blockDim.x) { cnt[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    auto group_of = [&](int p) {
+        const int m = p / q.ns, slot = p - m * q.ns;
+        if (slot >= q.topk) return q.E;
+        const int e = sel[(size_t)m * q.topk + slot];
+        return e < 0 ? 0 : (e >= q.E ? q.E - 1 : e);
+    };
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[group_of(p)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, j = 0;
+        for (int e = 0; e < G; ++e) { off[e] = o; jstart[e] = j; o += cnt[e]; j += (cnt[e] + 7) >> 3; }
+        total_jobs = j;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = group_of(p);
+        posof[p] = off[e] + atomicAdd(&cursor[e], 1);
+    }
+    for (int e = threadIdx.x; e < G; e += blockDim.x) {
+        const b200_nvfp4_mat* mats = e < q.E ? q.experts + (size_t)e * 3 : q.shared;
+        const unsigned char* mp = q.maps + (size_t)e * 6 * 128;
+        for (int c = 0; c * 8 < cnt[e]; ++c) {
+            const int idx = jstart[e] + c, rows = min(8, cnt[e] - 8 * c);
+            const size_t pos0 = (size_t)off[e] + 8 * c;
+            float* g = q.gbuf + pos0 * q.I;
+            float* u = q.ubuf + pos0 * q.I;
+            // the chunk's rows are split once (k_split_rows) for all the CTAs of its jobs
+            unsigned char* b1 = img1 + (size_t)idx * (q.H >> 8) * 8192;
+            unsigned char* b2 = img2 + (size_t)idx * (q.I >> 8) * 8192;
+            float* ga1 = gam1 + (size_t)idx * 64;
+            float* ga2 = gam2 + (size_t)idx * 64;
+            s1[idx] = SplitJob{xg + pos0 * q.H, nullptr, b1, ga1, rows, 0};
+            s2[idx] = SplitJob{g, u, b2, ga2, rows, 0};
+            q.j1[2 * idx] = UmJob{g, nullptr, nullptr, mats[0].gscale, mp, mp + 128, b1, ga1, q.I, rows, 0, 0};
+            q.j1[2 * idx + 1] = UmJob{u, nullptr, nullptr, mats[1].gscale, mp + 256, mp + 384, b1, ga1, q.I, rows, 0, 0};
+            q.j2[idx] = UmJob{q.part + pos0 * q.H, nullptr, nullptr, mats[2].gscale, mp + 512, mp + 640, b2, ga2, q.H, rows, 0, 0};
+        }
+    }
+    for (int idx = total_jobs + threadIdx.x; idx < max_jobs; idx += blockDim.x) {
+        const UmJob none{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+        q.j1[2 * idx] = none; q.j1[2 * idx + 1] = none; q.j2[idx] = none;
+        s1[idx] = SplitJob{nullptr, nullptr, nullptr, nullptr, 0, 0}; s2[idx] = s1[idx];
+    }
+}
+
+// xg[posof[p], :] = x[token of pair p, :]
+__global__ void k_moe_gather(float* __restrict__ xg, const float* __restrict__ x, const int* __restrict__ posof,
+                             int pairs, int ns, int H) {
+    const int per = H >> 2;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)pairs * per) return;
+    const int p = (int)(i / per), h4 = (int)(i - (size_t)p * per);
+    reinterpret_cast<float4*>(xg)[(size_t)posof[p] * per + h4] = reinterpret_cast<const float4*>(x)[(size_t)(p / ns) * per + h4];
+}
+
 static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
-// Scratch of the tensor-core path behind the logits: job tables | gate products | up products | down products.
+static int grouped_max_jobs(const b200_moe_layer* L, int M) { return (M * (L->topk + 1) + 7) / 8 + L->n_expert + 1; }
+
+// Scratch of the tensor-core path behind the logits.  Up to 8 tokens: job tables | gate products |
+// up products | down products, one row per (token, slot) pair.  More: pair positions | job tables |
+// gathered activations | gate | up | down products, rows grouped by expert.
 size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
     const size_t ns = (size_t)L->topk + 1, pairs = (size_t)M * ns;
-    return up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4);
+    if (M <= MU_MAX_TOKENS)
+        return up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4);
+    const size_t mj = (size_t)grouped_max_jobs(L, M);
+    return up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
+           up256(mj * (L->hidden >> 8) * 8192) + up256(mj * (L->inter >> 8) * 8192) +
+           2 * up256(pairs * L->hidden * 4) + 2 * up256(pairs * L->inter * 4);
 }
 
 // Fills `q` for a call on a prepared layer.  B200_ENOTIMPL: not prepared, too many tokens, or an
@@ -112,9 +196,49 @@ int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, i
     return B200_OK;
 }
 
-// The experts of a planned call.  planned: the job tables were already written (by the router).
+// More than 8 tokens on a prepared layer.
+static int moe_umma_grouped(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                            void* scratch, int M, cudaStream_t s) {
+    if (((uintptr_t)x & 15) || L->n_expert + 1 > MG_MAX_GROUPS) return B200_ENOTIMPL;
+    const Prepared* P = find_prepared(L);
+    if (!P) return B200_ENOTIMPL;
+    const int ns = L->topk + (L->shared ? 1 : 0), pairs = M * ns, H = L->hidden, I = L->inter;
+    const int max_jobs = grouped_max_jobs(L, M);
+    const size_t np = (size_t)M * (L->topk + 1);     // the sizes the workspace was laid out with
+    char* w = static_cast<char*>(scratch);
+    int* posof = reinterpret_cast<int*>(w); w += up256(np * 4);
+    MoePlan q{};
+    q.j1 = reinterpret_cast<UmJob*>(w); q.j2 = q.j1 + (size_t)2 * max_jobs; w += up256((size_t)max_jobs * 3 * sizeof(UmJob));
+    SplitJob* s1 = reinterpret_cast<SplitJob*>(w); w += up256((size_t)max_jobs * sizeof(SplitJob));
+    SplitJob* s2 = reinterpret_cast<SplitJob*>(w); w += up256((size_t)max_jobs * sizeof(SplitJob));
+    float* gam1 = reinterpret_cast<float*>(w); w += up256((size_t)max_jobs * 64 * 4);
+    float* gam2 = reinterpret_cast<float*>(w); w += up256((size_t)max_jobs * 64 * 4);
+    unsigned char* img1 = reinterpret_cast<unsigned char*>(w); w += up256((size_t)max_jobs * (H >> 8) * 8192);
+    unsigned char* img2 = reinterpret_cast<unsigned char*>(w); w += up256((size_t)max_jobs * (I >> 8) * 8192);
+    float* xg = reinterpret_cast<float*>(w); w += up256(np * H * 4);
+    q.part = reinterpret_cast<float*>(w); w += up256(np * H * 4);
+    q.gbuf = reinterpret_cast<float*>(w); w += up256(np * I * 4);
+    q.ubuf = reinterpret_cast<float*>(w);
+    q.experts = L->experts; q.shared = L->shared; q.maps = P->maps; q.x = x;
+    q.topk = L->topk; q.ns = ns; q.E = L->n_expert; q.H = H; q.I = I;
+    k_moe_group<<<1, 1024, 0, s>>>(q, sel, posof, xg, s1, s2, img1, img2, gam1, gam2, M, max_jobs);
+    if (int rc = check_launch("k_moe_group")) return rc;
+    const size_t n4 = (size_t)pairs * (H >> 2);
+    k_moe_gather<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(xg, x, posof, pairs, ns, H);
+    if (int rc = check_launch("k_moe_gather")) return rc;
+    if (int rc = umma_split_launch(s1, max_jobs, H, 0.f, s)) return rc;
+    if (int rc = umma_table_launch(q.j1, 2 * max_jobs, I, H, P->R_gu, 0.f, 8, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_split_launch(s2, max_jobs, I, L->swiglu_limit, s)) return rc;
+    if (int rc = umma_table_launch(q.j2, max_jobs, H, I, P->R_d, L->swiglu_limit, 8, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    const int y4 = M * (H >> 2);
+    k_moe_combine<<<(y4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, posof, M, q.topk, ns, H);
+    return check_launch("k_moe_combine");
+}
+
+// The experts of a call on a prepared layer.  planned: the job tables were already written (by the router).
 int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
                      void* scratch, int M, cudaStream_t s, bool planned) {
+    if (M > MU_MAX_TOKENS) return moe_umma_grouped(x, L, y, sel, wts, scratch, M, s);
     MoePlan q{};
     int R_gu = 0, R_d = 0;
     if (int rc = moe_umma_plan_args(x, L, scratch, M, &q, &R_gu, &R_d)) return rc;
@@ -123,10 +247,10 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
         k_moe_plan<<<(pairs + 127) / 128, 128, 0, s>>>(q, sel, M);
         if (int rc = check_launch("k_moe_plan")) return rc;
     }
-    if (int rc = umma_table_launch(q.j1, 2 * pairs, q.I, q.H, R_gu, 0.f, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
-    if (int rc = umma_table_launch(q.j2, pairs, q.H, q.I, R_d, L->swiglu_limit, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_table_launch(q.j1, 2 * pairs, q.I, q.H, R_gu, 0.f, 1, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_table_launch(q.j2, pairs, q.H, q.I, R_d, L->swiglu_limit, 1, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
     const int n4 = M * (q.H >> 2);
-    k_moe_combine<<<(n4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, M, q.topk, q.ns, q.H);
+    k_moe_combine<<<(n4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, nullptr, M, q.topk, q.ns, q.H);
     return check_launch("k_moe_combine");
 }
 

@@ -42,6 +42,8 @@ class RankLayer:
         self.l_route.n_expert = E
         self.l_local = B.MoeLayer(self.router, self.bias, self.local, None, 1, H, I)
         self.l_shared = B.MoeLayer(self.router, self.bias, [self.shared_w], None, 1, H, I)
+        # descriptors for the tensor-core experts (rows grouped by local expert); False = geometry unsuitable
+        self.tensor_core = B.moe_prepare(self.l_local) and B.moe_prepare(self.l_shared)
         self.ep = ExpertParallelMoE(E, topk, H, self.route, self.compute, self.shared, group)
         self.expert_bytes = 3 * (I * H // 2 + I * H // 16 + 4)
 

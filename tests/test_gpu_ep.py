@@ -18,6 +18,7 @@ def test_ep_world1_equals_moe_forward():
     y, sel, wts = L.forward(x)
     full = [P.ep_gpu.expert_weights(7, 0, e, H, I, dev) for e in range(E + 1)]
     ref = P.MoeLayer(L.router, L.bias, full[:E], full[E], topk, H, I)
+    assert L.tensor_core and P.moe_prepare(ref)        # both sides on the tensor-core experts
     y_ref, sel_ref, wts_ref = P.moe_forward(ref, x)
     assert torch.equal(sel, sel_ref) and torch.equal(wts, wts_ref)
     assert ((y - y_ref).norm() / y_ref.norm()).item() < 1e-5

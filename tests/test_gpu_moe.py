@@ -164,6 +164,32 @@ def test_moe_prepared_layer_runs_tensor_core_experts(H, I, E, M, shared):
     assert torch.equal(y_after, y_cc)
 
 
+@pytest.mark.parametrize('H,I,E,M,topk,shared', [(1024, 512, 32, 20, 8, True), (1024, 512, 8, 75, 1, False), (4096, 1536, 144, 33, 8, True)])
+def test_moe_prepared_layer_groups_rows_by_expert_beyond_8_tokens(H, I, E, M, topk, shared):
+    """More than 8 tokens on a prepared layer: pairs are sorted by expert on the device and every
+    expert runs chunks of up to 8 rows.  Same bar as the small-batch path, and every token still
+    equals that token alone (which takes the small-batch path) bit for bit."""
+    P, O = pkg(), oracle()
+    layer, d = build_layer(H, I, E, topk, seed=90 + M, shared=shared, on_gpu=H > 1024)
+    x = np.random.default_rng(M + I).normal(0, 1, (M, H)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y_cc, sel_cc, _ = P.moe_forward(layer, xd)
+    assert P.moe_prepare(layer)
+    try:
+        y, sel, wts = check_layer(layer, d, x)
+        assert torch.equal(sel, sel_cc)
+        assert not torch.equal(y, y_cc)
+        assert O.rel_l2(y.cpu().numpy(), y_cc.cpu().numpy()) <= REL_TOL
+        for m in (0, M // 2, M - 1):
+            y1, _, _ = P.moe_forward(layer, xd[m:m + 1].contiguous())
+            assert torch.equal(y1[0], y[m]), m
+        assert torch.equal(P.moe_experts(layer, xd, sel, wts), y)
+        assert torch.equal(P.moe_forward(layer, xd)[0], y)
+        assert P.device_status() == 0
+    finally:
+        P.moe_release(layer)
+
+
 def test_moe_prepare_refuses_unsuitable_geometry():
     P = pkg()
     layer, _ = build_layer(1056, 544, 8, 2, seed=3)   # not multiples of 256
