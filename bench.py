@@ -433,7 +433,7 @@ def main():
                                        'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
     if want('moe'):
         layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4000)
-        for M, prep in ((1, True), (4, True), (8, True), (1, False)):
+        for M, prep in ((1, True), (4, True), (8, True), (64, True), (1, False)):
             m, b, d = bench_moe(P, layers, M, sub_steps, a.warmup, prep)
             sub['moe_layer_I1536_M%d%s' % (M, '' if prep else '_cuda_core')] = {
                 'us_per_layer': m * 1e3, 'bytes': b, 'distinct_routed': d, 'tbps': b / (m * 1e-3) / 1e12,
