@@ -1,5 +1,5 @@
-// moe_umma.cu -- the MoE experts on the tensor-core gemv kernel (gemv_umma.cu), for decode batches
-// of up to 8 tokens, once b200_moe_prepare() has been called for the layer.
+// moe_umma.cu -- the MoE experts on the tensor-core gemv kernel (gemv_umma.cu), once
+// b200_moe_prepare() has been called for the layer.
 //
 // The expert tables of a layer live in device memory and the router picks experts on the device,
 // but a TMA tensor map has to be encoded on the host.  b200_moe_prepare therefore reads the
@@ -10,9 +10,12 @@
 // Launches per layer: router logits, k_route, k_moe_plan, gate+up products of all pairs (one
 // tensor-core launch), down products (one tensor-core launch; it reads the two products and
 // applies the clamped SwiGLU while it splits its activation vector), k_moe_combine.
-// Every (token, slot) pair is its own single-row job, the shared expert included (its weights
-// are read once from HBM and then from L2): a token's result does not depend on what else is
-// in the batch, bit for bit.  The gate-weighted sum runs over the slots in slot order.
+// Up to 8 tokens every (token, slot) pair is its own single-row job, the shared expert included
+// (its weights are read once from HBM and then from L2).  Beyond 8 tokens the pairs are sorted by
+// expert on the device and an expert's rows run in chunks of up to 8, each chunk split into its
+// FP4 digit image once (k_split_rows).  Either way a row is computed on its own: a token's result
+// does not depend on what else is in the batch, bit for bit.  The gate-weighted sum runs over
+// the slots in slot order.
 #include "b200_internal.h"
 #include "moe_plan.cuh"
 #include <cstdio>

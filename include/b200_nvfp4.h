@@ -138,7 +138,8 @@ int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t*
                      float* wts, void* ws, int M, b200_stream stream);
 
 /* Optional, once per layer after its weights are on the device: lets b200_moe_forward and
- * b200_moe_experts run batches of up to 8 tokens on the tensor-core kernels.  It reads the layer's
+ * b200_moe_experts run their experts on the tensor-core kernels (every pair on its own up to 8
+ * tokens, rows grouped by expert beyond).  It reads the layer's
  * device-side expert tables (a synchronous copy: call it at load time, never under stream
  * capture), encodes TMA descriptors for every expert and keeps them in device memory until
  * b200_moe_release or process exit.  The layer is recognised later by its experts / shared

@@ -31,7 +31,7 @@ struct MoeLayer {
 // Not in the reference: layer geometry used by every call below (defaults = reference constants).
 void moe_set_geometry(int hidden, int inter, float routed_scale, float swiglu_limit, bool norm_topk);
 // Not in the reference: once per layer after its tables are built (src/engine.cu:168-195 is the
-// place), so that decode batches of up to 8 tokens run their experts on the tensor-core kernels.
+// place), so that moe_forward* run their experts on the tensor-core kernels.
 // Synchronous (reads the tables back); false = the layer's geometry or alignment does not suit
 // them and it keeps the CUDA-core kernels.  moe_release drops what moe_prepare built.
 bool moe_prepare(const MoeLayer& L);
