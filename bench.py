@@ -341,7 +341,7 @@ def bench_ep(P, a, rank, local, world, peak):
                      'frac': val * 1e3 / world / peak, 'traffic': None},
         'e2e': {'value': total_b / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': Tl * H * 4 * world, 'd2h_bytes_per_step': Tl * H * 4 * world},
-        'gpu_launches': a.steps * Lyr * 6, 'clocks': cs.summary(), 'ep_parity_vs_single_gpu': par, 'rank0_layer_stats': stats,
+        'gpu_launches': a.steps * Lyr * (16 if layers[0].tensor_core else 6), 'device_status': P.device_status(), 'clocks': cs.summary(), 'ep_parity_vs_single_gpu': par, 'rank0_layer_stats': stats,
         'cpu_baseline': None,
     }))
 
@@ -462,7 +462,7 @@ def main():
         'cpu_baseline': {'value': nbytes / cpu_s / 1e12, 'unit': 'TB/s', 'cores': torch.get_num_threads(),
                          'kind': 'port', 'sample': '%d steps of the same six-sibling workload, torch dequantise + linear' % cpu_n,
                          'ms_per_step': cpu_s * 1e3},
-        'gpu_launches': a.steps, 'clocks': clocks, 'sub': sub,
+        'gpu_launches': a.steps, 'device_status': P.device_status(), 'clocks': clocks, 'sub': sub,
     }
     print(json.dumps(out))
 

@@ -22,16 +22,21 @@ __global__ void __launch_bounds__(256)
 k_amax_bf16(const uint4* __restrict__ w, size_t n_vec, const __nv_bfloat16* __restrict__ tail,
             size_t n_tail, uint32_t* __restrict__ out_bits) {
     float a = 0.f;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const uint4 v = w[i];
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    auto fold = [&](const uint4& v) {
         const uint32_t u[4] = {v.x, v.y, v.z, v.w};
         #pragma unroll
         for (int j = 0; j < 4; ++j) {
             a = fmaxf(a, fabsf(__uint_as_float(u[j] << 16)));
             a = fmaxf(a, fabsf(__uint_as_float(u[j] & 0xffff0000u)));
         }
+    };
+    for (; i + 3 * stride < n_vec; i += 4 * stride) {           // four loads in flight per thread
+        const uint4 v0 = w[i], v1 = w[i + stride], v2 = w[i + 2 * stride], v3 = w[i + 3 * stride];
+        fold(v0); fold(v1); fold(v2); fold(v3);
     }
+    for (; i < n_vec; i += stride) fold(w[i]);
     if (blockIdx.x == 0)
         for (size_t i = threadIdx.x; i < n_tail; i += blockDim.x) a = fmaxf(a, fabsf(__bfloat162float(tail[i])));
     a = warp_max(a);
@@ -56,51 +61,76 @@ __device__ __forceinline__ int e2m1_index(float a) {          // #{mid < a}, mid
     return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
 }
 
+// One 16-group: scale code and sixteen e2m1 codes, fp32 IEEE operations in the reference's order.
+__device__ __forceinline__ void quantize_group(const float (&v)[16], float gs, uint32_t& lo, uint32_t& hi, int& code) {
+    float amax = 0.f;
+    #pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
+    s = fminf(fmaxf(s, 0.f), 448.f);
+    code = e4m3_floor_code(s);
+    if (code < 126) {
+        const float mid = __fmul_rn(__fadd_rn(e4m3_to_f32(code + 1), e4m3_to_f32(code)), 0.5f);
+        code += (mid < s) ? 1 : 0;
+    }
+    const float eff = fmaxf(__fdiv_rn(e4m3_to_f32(code), gs), 1e-30f);
+    lo = 0; hi = 0;
+    #pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float q = __fdiv_rn(v[j], eff);
+        uint32_t c = (uint32_t)e2m1_index(fabsf(q));
+        if (c != 0 && (__float_as_uint(q) >> 31)) c |= 8u;
+        if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
+    }
+}
+__device__ __forceinline__ void unpack_bf16x16(const uint4& a, const uint4& b, float (&v)[16]) {
+    const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    #pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[2 * j] = __uint_as_float(u[j] << 16);
+        v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void store_group(uint8_t* packed, uint8_t* scale, size_t g, uint32_t lo, uint32_t hi, int code, bool vec_out) {
+    if (vec_out) {
+        reinterpret_cast<uint2*>(packed)[g] = make_uint2(lo, hi);
+    } else {
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) { packed[8 * g + j] = (uint8_t)(lo >> (8 * j)); packed[8 * g + 4 + j] = (uint8_t)(hi >> (8 * j)); }
+    }
+    scale[g] = (uint8_t)code;
+}
+
 __global__ void __launch_bounds__(256)
 k_quantize(const __nv_bfloat16* __restrict__ w, size_t n_groups, const float* __restrict__ gsp,
            uint8_t* __restrict__ packed, uint8_t* __restrict__ scale, bool vec_in, bool vec_out) {
     const float gs = gsp[0];
-    for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups;
-         g += (size_t)gridDim.x * blockDim.x) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec_in) {
+        const uint4* wv = reinterpret_cast<const uint4*>(w);
+        for (; g + stride < n_groups; g += 2 * stride) {         // two groups per trip: four loads in flight, two chains
+            const uint4 a0 = wv[2 * g], b0 = wv[2 * g + 1], a1 = wv[2 * (g + stride)], b1 = wv[2 * (g + stride) + 1];
+            float v0[16], v1[16];
+            unpack_bf16x16(a0, b0, v0); unpack_bf16x16(a1, b1, v1);
+            uint32_t lo0, hi0, lo1, hi1; int c0, c1;
+            quantize_group(v0, gs, lo0, hi0, c0);
+            quantize_group(v1, gs, lo1, hi1, c1);
+            store_group(packed, scale, g, lo0, hi0, c0, vec_out);
+            store_group(packed, scale, g + stride, lo1, hi1, c1, vec_out);
+        }
+    }
+    for (; g < n_groups; g += stride) {
         float v[16];
         if (vec_in) {
-            const uint4 a = reinterpret_cast<const uint4*>(w)[2 * g], b = reinterpret_cast<const uint4*>(w)[2 * g + 1];
-            const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[2 * j] = __uint_as_float(u[j] << 16);
-                v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-            }
+            unpack_bf16x16(reinterpret_cast<const uint4*>(w)[2 * g], reinterpret_cast<const uint4*>(w)[2 * g + 1], v);
         } else {
             #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(w[16 * g + j]);
         }
-        float amax = 0.f;
-        #pragma unroll
-        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
-        s = fminf(fmaxf(s, 0.f), 448.f);
-        int code = e4m3_floor_code(s);
-        if (code < 126) {
-            const float mid = __fmul_rn(__fadd_rn(e4m3_to_f32(code + 1), e4m3_to_f32(code)), 0.5f);
-            code += (mid < s) ? 1 : 0;
-        }
-        const float eff = fmaxf(__fdiv_rn(e4m3_to_f32(code), gs), 1e-30f);
-        uint32_t lo = 0, hi = 0;
-        #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float q = __fdiv_rn(v[j], eff);
-            uint32_t c = (uint32_t)e2m1_index(fabsf(q));
-            if (c != 0 && (__float_as_uint(q) >> 31)) c |= 8u;
-            if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
-        }
-        if (vec_out) {
-            reinterpret_cast<uint2*>(packed)[g] = make_uint2(lo, hi);
-        } else {
-            #pragma unroll
-            for (int j = 0; j < 4; ++j) { packed[8 * g + j] = (uint8_t)(lo >> (8 * j)); packed[8 * g + 4 + j] = (uint8_t)(hi >> (8 * j)); }
-        }
-        scale[g] = (uint8_t)code;
+        uint32_t lo, hi; int code;
+        quantize_group(v, gs, lo, hi, code);
+        store_group(packed, scale, g, lo, hi, code, vec_out);
     }
 }
 

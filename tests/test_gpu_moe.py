@@ -190,6 +190,33 @@ def test_moe_prepared_layer_groups_rows_by_expert_beyond_8_tokens(H, I, E, M, to
         P.moe_release(layer)
 
 
+def test_moe_prepared_layer_under_graph_capture():
+    """The prepared path only launches kernels (descriptor look-up is host-side), so a layer forward
+    can be captured and replayed; small-batch and grouped paths."""
+    P = pkg()
+    layer, d = build_layer(1024, 512, 32, 8, seed=123)
+    assert P.moe_prepare(layer)
+    try:
+        for M in (2, 19):
+            x = torch.randn((M, 1024), device='cuda')
+            want, sel_w, _ = P.moe_forward(layer, x)
+            y = torch.zeros_like(want); sel = torch.zeros_like(sel_w); wts = torch.zeros((M, 8), device='cuda')
+            st = torch.cuda.Stream()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(st):
+                P.moe_forward(layer, x, y, sel, wts)          # warm-up on the capture stream (workspace, attributes)
+                st.synchronize()
+                with torch.cuda.graph(g, stream=st):
+                    for _ in range(3): P.moe_forward(layer, x, y, sel, wts)
+            y.zero_()
+            g.replay(); g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y, want) and torch.equal(sel, sel_w), M
+        assert P.device_status() == 0
+    finally:
+        P.moe_release(layer)
+
+
 def test_moe_prepare_refuses_unsuitable_geometry():
     P = pkg()
     layer, _ = build_layer(1056, 544, 8, 2, seed=3)   # not multiples of 256
