@@ -156,33 +156,36 @@ def bench_siblings(P, M, steps, warmup, copies, sampler_index=None):
     base = [make_weight(P, n, K_HID, 1000 + i)[0] for i, n in enumerate(SIBLINGS)]
     sets = [base] + [[clone_weight(P, W) for W in base] for _ in range(copies - 1)]
     x = torch.randn((M, K_HID), device='cuda', generator=torch.Generator(device='cuda').manual_seed(2))
-    ys = [torch.empty((M, n), device='cuda') for n in SIBLINGS]
+    ybuf = torch.empty(M * sum(SIBLINGS), device='cuda')       # the six outputs side by side: one copy brings them all back
+    ys, o = [], 0
+    for n in SIBLINGS:
+        ys.append(ybuf[o:o + M * n].view(M, n)); o += M * n
     jobs = [P.make_jobs(ws, [x] * 6, ys) for ws in sets]
-    fns = [lambda ws=ws, j=j: P.gemv_multi(ws, x, M, ys, jobs=j) for ws, j in zip(sets, jobs)]
+    split = P.split_workspace(M, K_HID, x.device) if M > 1 else None       # activations split once per call (the *_ws entry points)
+    fns = [lambda ws=ws, j=j: P.gemv_multi(ws, x, M, ys, jobs=j, ws=split) for ws, j in zip(sets, jobs)]
     nbytes = sum(nv_bytes(n, K_HID) for n in SIBLINGS) + M * K_HID * 4 + M * sum(SIBLINGS) * 4
     if sampler_index is None:
         ms = time_steps(fns, steps, warmup)
-        return ms, nbytes, None, (sets, x, ys, jobs)
+        return ms, nbytes, None, (sets, x, ys, jobs, ybuf)
     with ClockSampler(sampler_index) as cs:
         ms = time_steps(fns, steps, warmup)
         if steps * ms < 400:                        # keep the region long enough to be sampled
             time_steps(fns, int(400 / max(ms, 1e-3)), 0)
-    return ms, nbytes, cs.summary(), (sets, x, ys, jobs)
+    return ms, nbytes, cs.summary(), (sets, x, ys, jobs, ybuf)
 
 
 def bench_siblings_e2e(P, state, steps, warmup):
-    """Host buffers: x from pinned memory in, six outputs back to pinned memory, per step."""
-    sets, x, ys, jobs = state
+    """Host buffers: x from pinned memory in, the six outputs (one device buffer) back to pinned memory, per step."""
+    sets, x, ys, jobs, ybuf = state
     M = x.shape[0]
     xh = torch.randn((M, K_HID)).pin_memory()
-    yh = [torch.empty((M, n)).pin_memory() for n in SIBLINGS]
+    yh = torch.empty(ybuf.shape).pin_memory()
     s = torch.cuda.current_stream()
 
     def step(i):
         x.copy_(xh, non_blocking=True)
         P.gemv_multi(sets[i % len(sets)], x, M, ys, jobs=jobs[i % len(sets)])
-        for a, b in zip(yh, ys):
-            a.copy_(b, non_blocking=True)
+        yh.copy_(ybuf, non_blocking=True)
         s.synchronize()                            # the caller reads the result every step
     for i in range(warmup):
         step(i)
@@ -203,6 +206,19 @@ def bench_gemv_single(P, steps, warmup, copies):
     y = torch.empty((1, N), device='cuda')
     ms = time_steps([lambda W=W: P.gemm(W, x, y) for W in ws], steps, warmup)
     return ms, nv_bytes(N, K_HID) + K_HID * 4 + N * 4
+
+
+def bench_gemm_batch(P, M, steps, warmup, copies):
+    """[12288 x 4096] NVFP4 weights against M activation rows (a prefill-sized batch runs as passes of 8
+    rows over the weights).  Returns ms and the FLOPs of one call."""
+    N = 12288
+    base, _ = make_weight(P, N, K_HID, 998)
+    ws = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
+    x = torch.randn((M, K_HID), device='cuda')
+    y = torch.empty((M, N), device='cuda')
+    split = P.split_workspace(M, K_HID, x.device)
+    ms = time_steps([lambda W=W: P.gemm(W, x, y, ws=split) for W in ws], steps, warmup)
+    return ms, 2.0 * M * N * K_HID
 
 
 def build_moe_layers(P, n_layers, H, I, E, topk, seed):
@@ -365,7 +381,7 @@ def cpu_siblings_step(host_sets, x):
 
 
 def cpu_baseline(P, state, max_seconds=20.0):
-    sets, x, _, _ = state
+    sets, x = state[0], state[1]
     host = [(W.packed.cpu(), W.scale.cpu().view(torch.float8_e4m3fn), W.gscale.cpu()) for W in sets[0]]
     xh = x.cpu()
     cpu_siblings_step(host, xh)                       # warm-up
@@ -431,6 +447,10 @@ def main():
             m, b, _, _ = bench_siblings(P, M, sub_steps, a.warmup, copies)
             sub['siblings_M%d' % M] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
                                        'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    if want('gemm'):
+        for M in (32, 128):
+            m, fl = bench_gemm_batch(P, M, max(20, sub_steps // 10), a.warmup, copies)
+            sub['gemm_12288x4096_M%d' % M] = {'us': m * 1e3, 'tflops': fl / (m * 1e-3) / 1e12, 'passes_of_8_rows': M // 8}
     if want('moe'):
         layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4000)
         for M, prep in ((1, True), (4, True), (8, True), (64, True), (1, False)):

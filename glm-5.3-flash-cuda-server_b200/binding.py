@@ -53,6 +53,9 @@ def lib():
         L.b200_nvfp4_device_status.argtypes = [C.POINTER(C.c_uint), ci]
         L.b200_nvfp4_gemm.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp]
         L.b200_nvfp4_gemv_multi.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp]
+        L.b200_nvfp4_split_workspace_bytes.restype = st; L.b200_nvfp4_split_workspace_bytes.argtypes = [ci, ci]
+        L.b200_nvfp4_gemm_ws.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp, vp]
+        L.b200_nvfp4_gemv_multi_ws.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp, vp]
         L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
         L.b200_bf16_to_f32.argtypes = [vp, vp, st, vp]
         L.b200_nvfp4_quantize.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
@@ -70,7 +73,7 @@ def lib():
 
 
 ENOTIMPL = 6
-EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi',
+EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
            'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
            'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release']
@@ -126,8 +129,13 @@ class Nvfp4Weight:
         return self.packed.numel() + self.scale.numel() + 4
 
 
-def gemm(W, x, y=None, dtype=BF16, stream=None):
-    """y[M,N] = x[M,K] . W^T.  W: Nvfp4Weight, or a bf16/f32 torch tensor [N,K]."""
+def split_workspace(M, K, device):
+    """Scratch for gemm(..., ws=) / gemv_multi(..., ws=): the pre-split activation images."""
+    return torch.empty(lib().b200_nvfp4_split_workspace_bytes(M, K), dtype=torch.uint8, device=device)
+
+
+def gemm(W, x, y=None, dtype=BF16, stream=None, ws=None):
+    """y[M,N] = x[M,K] . W^T.  W: Nvfp4Weight, or a bf16/f32 torch tensor [N,K].  ws: split_workspace(M, K)."""
     x2 = x if x.dim() == 2 else x.unsqueeze(0)
     M, K = x2.shape
     if isinstance(W, Nvfp4Weight):
@@ -138,7 +146,10 @@ def gemm(W, x, y=None, dtype=BF16, stream=None):
         dtype = F32 if W.dtype == torch.float32 else BF16
     if y is None:
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
-    check(lib().b200_nvfp4_gemm(_ptr(y), C.byref(ref), _ptr(x2), M, N, K, dtype, stream_ptr(stream)), 'b200_nvfp4_gemm')
+    if ws is not None:
+        check(lib().b200_nvfp4_gemm_ws(_ptr(y), C.byref(ref), _ptr(x2), M, N, K, dtype, _ptr(ws), stream_ptr(stream)), 'b200_nvfp4_gemm_ws')
+    else:
+        check(lib().b200_nvfp4_gemm(_ptr(y), C.byref(ref), _ptr(x2), M, N, K, dtype, stream_ptr(stream)), 'b200_nvfp4_gemm')
     return y if x.dim() == 2 else y[0]
 
 
@@ -153,7 +164,7 @@ def make_jobs(weights, xs, ys):
     return arr
 
 
-def gemv_multi(weights, xs, M=1, ys=None, stream=None, jobs=None):
+def gemv_multi(weights, xs, M=1, ys=None, stream=None, jobs=None, ws=None):
     """Fused group: weights share K; xs is one tensor [M,K] (shared) or a list (one per job)."""
     if not isinstance(xs, (list, tuple)):
         xs = [xs] * len(weights)
@@ -161,7 +172,10 @@ def gemv_multi(weights, xs, M=1, ys=None, stream=None, jobs=None):
         ys = [torch.empty((M, W.N), dtype=torch.float32, device=xs[0].device) for W in weights]
     if jobs is None:
         jobs = make_jobs(weights, xs, ys)
-    check(lib().b200_nvfp4_gemv_multi(jobs, len(weights), M, weights[0].K, BF16, stream_ptr(stream)), 'b200_nvfp4_gemv_multi')
+    if ws is not None:
+        check(lib().b200_nvfp4_gemv_multi_ws(jobs, len(weights), M, weights[0].K, BF16, _ptr(ws), stream_ptr(stream)), 'b200_nvfp4_gemv_multi_ws')
+    else:
+        check(lib().b200_nvfp4_gemv_multi(jobs, len(weights), M, weights[0].K, BF16, stream_ptr(stream)), 'b200_nvfp4_gemv_multi')
     return ys
 
 

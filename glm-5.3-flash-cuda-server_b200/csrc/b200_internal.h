@@ -30,7 +30,7 @@ struct GemvParams {
 };
 
 // gemv.cu
-int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s);
+int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s, void* split_ws);
 int dense_gemm(float* y, const void* W, const float* x, int M, int N, int K, int dtype, cudaStream_t s);
 int nvfp4_math_mode();
 
@@ -39,6 +39,8 @@ int nvfp4_math_mode();
 int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
 // gemv_umma.cu: single-row tensor-core (tcgen05 block-scaled) kernel; same contract.
 int nvfp4_multi_umma(const GemvParams& p, int M, cudaStream_t s);
+size_t umma_presplit_bytes(int M, int K);
+int nvfp4_multi_umma_ws(const GemvParams& p, int M, void* ws, cudaStream_t s);
 // One job of the tensor-core kernel: x [M, K], y [M, N].  x2 != nullptr: the activations are the
 // clamped SwiGLU of two vectors, x = silu(min(x, limit)) * clamp(x2, -limit, limit) (the MoE down
 // projection reads the gate and up products directly).  mw, ms: CUtensorMap of packed weights and

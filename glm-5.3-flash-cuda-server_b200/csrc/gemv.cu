@@ -281,7 +281,7 @@ static bool use_umma() {
 int rows_per_tile(int M) { return GEMV_WARPS * (M <= 2 ? 4 : 2); }
 
 // Validates, decides fast vs generic, builds the flat task list, launches.  n in 1..8, M in 1..8.
-int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s) {
+int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s, void* split_ws) {
     if (!jobs || n < 1 || n > B200_GEMV_MULTI_MAX || M < 1 || M > B200_GEMV_M_MAX) return B200_EINVAL;
     if (K <= 0 || (K & 15)) return B200_ESHAPE;
     GemvParams p{};
@@ -302,6 +302,10 @@ int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s) 
     for (int i = n; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].N = 0; p.j[i].task0 = 0x7fffffff; }
     p.total_tasks = tasks;
     if (use_umma() && !force_general()) {            // checks its own conditions; they do not depend on M
+        if (split_ws && M > 2) {                         // activations split once into the caller's scratch (pays from 3 rows on)
+            const int rc = nvfp4_multi_umma_ws(p, M, split_ws, s);
+            if (rc != B200_ENOTIMPL) return rc;
+        }
         const int rc = nvfp4_multi_umma(p, M, s);
         if (rc != B200_ENOTIMPL) return rc;
     }
@@ -375,11 +379,42 @@ extern "C" int b200_nvfp4_gemm(float* y, const b200_wref* W, const float* x, int
     for (int done = 0; done < M;) {
         const int c = std::min(M - done, (int)B200_GEMV_M_MAX);
         b200_gemv_job j{y + (size_t)done * N, *W, x + (size_t)done * K, N};
-        const int rc = nvfp4_multi(&j, 1, c, K, stream);
+        const int rc = nvfp4_multi(&j, 1, c, K, stream, nullptr);
         if (rc) return rc;
         done += c;
     }
     return B200_OK;
+}
+
+extern "C" size_t b200_nvfp4_split_workspace_bytes(int M, int K) {
+    if (M < 1 || K < 256) return 256;
+    return (umma_presplit_bytes(M, K) + 255) / 256 * 256;
+}
+
+extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, int M, int N, int K,
+                                  int dtype, void* ws, b200_stream stream) {
+    if (!W || M < 1) return B200_EINVAL;
+    if (!W->packed || !ws || M < 2) return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
+    if ((uintptr_t)ws & 255) return B200_EALIGN;
+    // every row at once: one split launch, then one pass over the weights per 8 rows
+    b200_gemv_job j{y, *W, x, N};
+    GemvParams p{};
+    if (!j.y || !j.x || !W->scale || !W->gscale || N <= 0 || K <= 0 || (K & 15)) return B200_EINVAL;
+    p.n_jobs = 1; p.K = K;
+    p.j[0] = GemvJobDev{j.y, W->packed, W->scale, W->gscale, j.x, N, 0};
+    for (int i = 1; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].N = 0; p.j[i].task0 = 0x7fffffff; }
+    const int rc = nvfp4_multi_umma_ws(p, M, ws, stream);
+    if (rc != B200_ENOTIMPL) return rc;
+    return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
+}
+
+extern "C" int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
+                                        void* ws, b200_stream stream) {
+    if (!jobs || n < 1 || n > B200_GEMV_MULTI_MAX || M < 1 || M > B200_GEMV_M_MAX) return B200_EINVAL;
+    if (ws && ((uintptr_t)ws & 255)) return B200_EALIGN;
+    for (int i = 0; i < n; ++i)
+        if (!jobs[i].W.packed) return b200_nvfp4_gemv_multi(jobs, n, M, K, dtype, stream);
+    return nvfp4_multi(jobs, n, M, K, stream, ws);
 }
 
 extern "C" int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
@@ -387,7 +422,7 @@ extern "C" int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, in
     if (!jobs || n < 1 || n > B200_GEMV_MULTI_MAX || M < 1 || M > B200_GEMV_M_MAX) return B200_EINVAL;
     bool all_q = true;
     for (int i = 0; i < n; ++i) all_q = all_q && jobs[i].W.packed != nullptr;
-    if (all_q) return nvfp4_multi(jobs, n, M, K, stream);
+    if (all_q) return nvfp4_multi(jobs, n, M, K, stream, nullptr);
     for (int i = 0; i < n; ++i) {                  // mixed or plain weights: correct, not fused
         const int rc = b200_nvfp4_gemm(jobs[i].y, &jobs[i].W, jobs[i].x, M, jobs[i].N, K, dtype, stream);
         if (rc) return rc;

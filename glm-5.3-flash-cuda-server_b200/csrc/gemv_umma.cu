@@ -72,6 +72,7 @@ struct UmParams {
     unsigned int* status;
     float limit;                                   // SwiGLU clamp for jobs with x2
     int n_jobs, K, R, stages, prefetch_before_wait, max_m, tiles_per_job;
+    int dry_run;                                   // host only: stop before the launch (does the shape fit?)
     int T;                                         // consecutive row tiles of one job per CTA (T * max_m <= 8, T * K/256 <= 64)
     uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
     int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
@@ -473,6 +474,20 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
 unsigned long long* g_trace_umma = nullptr;
 #endif
 
+// Pre-split activations of a gemm: chunk c (rows 8c..8c+7) has its image at img + c * chunk_bytes
+// (rows at `stride`) and its digit weights at gam + c * 64.
+struct PreSplit { unsigned char* img; float* gam; size_t chunk_bytes; int stride; int chunk; bool dry_run; };
+
+// One CTA per activation row of x [M, K].
+__global__ void __launch_bounds__(UM_WORKERS)
+k_split_x(const float* __restrict__ x, int K, int stride, unsigned char* __restrict__ img, size_t chunk_bytes, float* __restrict__ gam) {
+    __shared__ float red[UM_MAX_M][8];
+    pdl_wait();
+    const int m = blockIdx.x, c = m / UM_MAX_M, r = m - c * UM_MAX_M;
+    split_rows<false>(x + (size_t)m * K, nullptr, 0.f, 1, K, stride, img + (size_t)c * chunk_bytes + (size_t)r * 1024,
+                      gam + (size_t)c * UM_MAX_M * UM_NB + r * UM_NB, red, (int)threadIdx.x);
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -499,7 +514,7 @@ static bool make_map(CUtensorMap* m, const void* base, int rows, size_t row_byte
 
 // Conditions: M = 1 (one activation row shared by all jobs), K % 256 == 0 and K <= 16384, 16-byte
 // aligned tensors and activation, at least 256 rows in total.
-static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s);
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre);
 static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaStream_t s);
 static bool scale_box(int K, int* box, int* swz);
 
@@ -510,16 +525,50 @@ int nvfp4_multi_umma(const GemvParams& g, int M, cudaStream_t s) {
     if (M < 1) return B200_ENOTIMPL;
     int done = 0, cap = UM_MAX_M;                    // cap: the chunk size the first launch settled on
     while (done < M) {
-        int mc = std::min(cap, M - done), rc = umma_launch(g, mc, done, s);
-        while (rc == B200_ENOTIMPL && done == 0 && mc > 1) { mc /= 2; rc = umma_launch(g, mc, done, s); }
+        int mc = std::min(cap, M - done), rc = umma_launch(g, mc, done, s, nullptr);
+        while (rc == B200_ENOTIMPL && done == 0 && mc > 1) { mc /= 2; rc = umma_launch(g, mc, done, s, nullptr); }
         if (rc != B200_OK) return rc;                // ENOTIMPL only before anything was launched
         cap = mc; done += mc;
     }
     return B200_OK;
 }
 
+// The same with the activation rows split beforehand, once, into caller-supplied scratch: one
+// k_split_x launch for all M rows, then one pass per 8 rows whose CTAs copy their image in instead
+// of each splitting the rows again.  All jobs must share one activation matrix.
+size_t umma_presplit_bytes(int M, int K) {
+    const size_t chunks = ((size_t)M + UM_MAX_M - 1) / UM_MAX_M, stride = (size_t)std::min(M, UM_MAX_M);
+    return chunks * (size_t)(K / 256) * stride * 1024 + chunks * UM_MAX_M * UM_NB * 4;
+}
+int nvfp4_multi_umma_ws(const GemvParams& g, int M, void* ws, cudaStream_t s) {
+    const int K = g.K;
+    if (M < 2 || !ws || ((uintptr_t)ws & 255) || (K & 255) || K > 16384) return B200_ENOTIMPL;
+    for (int i = 0; i < g.n_jobs; ++i) if (g.j[i].x != g.j[0].x) return B200_ENOTIMPL;
+    if ((uintptr_t)g.j[0].x & 15) return B200_ENOTIMPL;
+    PreSplit pre{};
+    pre.stride = std::min(M, UM_MAX_M);
+    pre.chunk_bytes = (size_t)(K / 256) * pre.stride * 1024;
+    const int chunks = (M + UM_MAX_M - 1) / UM_MAX_M;
+    pre.img = static_cast<unsigned char*>(ws);
+    pre.gam = reinterpret_cast<float*>(pre.img + (size_t)chunks * pre.chunk_bytes);
+    // does a pass fit at all?  (asked before anything is launched, so that the caller can fall back)
+    {
+        pre.dry_run = true;
+        const int probe = umma_launch(g, std::min(M, UM_MAX_M), 0, s, &pre);
+        pre.dry_run = false;
+        if (probe != B200_OK) return probe;
+    }
+    k_split_x<<<M, UM_WORKERS, 0, s>>>(g.j[0].x, K, pre.stride, pre.img, pre.chunk_bytes, pre.gam);
+    if (int rc = check_launch("k_split_x")) return rc;
+    for (int done = 0; done < M; done += UM_MAX_M) {
+        pre.chunk = done / UM_MAX_M;
+        if (int rc = umma_launch(g, std::min(UM_MAX_M, M - done), done, s, &pre)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    }
+    return B200_OK;
+}
+
 // One launch: activation rows [m0, m0 + M) of every job.
-static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre) {
     const int K = g.K;
     if ((K & 255) || K > 16384 || !encode_fn()) return B200_ENOTIMPL;
     if (M < 1 || M > UM_MAX_M) return B200_ENOTIMPL;
@@ -534,11 +583,14 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s) {
     }
     static UmMaps maps;                              // one host thread at a time calls in
     UmParams p{};
-    p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = M; p.T = 1;
+    p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = pre ? pre->stride : M; p.T = 1;
+    p.dry_run = pre && pre->dry_run;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
-        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr, nullptr, nullptr, g.j[i].N, M, tasks, 0};
+        p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr,
+                       pre ? pre->img + (size_t)pre->chunk * pre->chunk_bytes : nullptr,
+                       pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0};
         tasks += (g.j[i].N + R - 1) / R;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
@@ -579,6 +631,7 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
       if (!tb) { cudaMalloc(&tb, 8 * 1024 * 64 * 8); cudaMemset(tb, 0, 8 * 1024 * 64 * 8); }
       p.trace = tb + (size_t)(cnt++ % 8) * 1024 * 64; g_trace_umma = tb; }
 #endif
+    if (p.dry_run) return B200_OK;
     const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
     static bool ready[2] = {false, false};
     if (!ready[gen]) {

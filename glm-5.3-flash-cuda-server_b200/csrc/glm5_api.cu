@@ -37,6 +37,18 @@ void gemm_multi(const GemvJob* jobs, int n, int M, int K, int dtype, cudaStream_
     must(b200_nvfp4_gemv_multi(j, n, M, K, dtype, s), "gemv_multi");
 }
 void gemv_multi(const GemvJob* jobs, int n, int K, int dtype, cudaStream_t s) { gemm_multi(jobs, n, 1, K, dtype, s); }
+size_t split_workspace_bytes(int M, int K) { return b200_nvfp4_split_workspace_bytes(M, K); }
+void gemm_ws(float* y, const WRef& W, const float* x, int M, int N, int K, int dtype, void* ws, cudaStream_t s) {
+    const b200_wref w = cw(W);
+    must(b200_nvfp4_gemm_ws(y, &w, x, M, N, K, dtype, ws, s), "gemm_ws");
+}
+void gemm_multi_ws(const GemvJob* jobs, int n, int M, int K, int dtype, void* ws, cudaStream_t s) {
+    if (n < 1) return;
+    if (n > GEMV_MULTI_MAX || M > B200_GEMV_M_MAX) { gemm_multi(jobs, n, M, K, dtype, s); return; }
+    b200_gemv_job j[B200_GEMV_MULTI_MAX];
+    for (int i = 0; i < n; ++i) j[i] = b200_gemv_job{jobs[i].y, cw(jobs[i].W), jobs[i].x, jobs[i].N};
+    must(b200_nvfp4_gemv_multi_ws(j, n, M, K, dtype, ws, s), "gemm_multi_ws");
+}
 void f32_to_bf16(void* dst, const float* src, size_t n, cudaStream_t s) { must(b200_f32_to_bf16(dst, src, n, s), "f32_to_bf16"); }
 void f32_from_bf16_dev(float* dst, const void* src, size_t n, cudaStream_t s) { must(b200_bf16_to_f32(dst, src, n, s), "f32_from_bf16_dev"); }
 

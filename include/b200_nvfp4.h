@@ -108,6 +108,21 @@ int b200_nvfp4_gemm(float* y, const b200_wref* W, const float* x, int M, int N, 
 int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
                           b200_stream stream);
 
+/* The two calls above with scratch from the caller, for M >= 2: the activation rows are split into
+ * their tensor-core operand image once, by one small launch into `ws`, instead of by every CTA of
+ * the product kernel (which is what makes rows beyond the first cost 2.4 us each otherwise).
+ * ws: b200_nvfp4_split_workspace_bytes(M, K) bytes of device memory, 256-byte aligned; only this
+ * call's kernels use it, so calls that may overlap on the GPU need separate scratch, and the
+ * next call on the same stream may reuse it.  Results are bit-identical to the plain calls.
+ * gemv_multi_ws wants all jobs to share one x; where the scratch cannot be used (M = 1, shapes the
+ * tensor-core kernel does not take, ws == NULL) these run exactly as the plain calls.  No
+ * counterpart in the reference, whose gemm has no workspace argument (include/gemv.h:75). */
+size_t b200_nvfp4_split_workspace_bytes(int M, int K);
+int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, int M, int N, int K,
+                       int dtype, void* ws, b200_stream stream);
+int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
+                             void* ws, b200_stream stream);
+
 /* Element-wise converters (reference include/gemv.h:61-62, kernels/gemv.cu:470-488). */
 int b200_f32_to_bf16(void* dst_bf16, const float* src, size_t n, b200_stream stream);
 int b200_bf16_to_f32(float* dst, const void* src_bf16, size_t n, b200_stream stream);

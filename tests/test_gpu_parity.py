@@ -201,6 +201,31 @@ def test_tensor_core_gemv_vs_oracle_and_row_invariance(N, K, M):
     assert P.device_status() == 0
 
 
+@pytest.mark.parametrize('N,K,M', [(1000, 4096, 2), (4096, 1024, 8), (700, 1536, 5), (300, 2048, 20), (129, 4096, 64), (300, 16384, 8), (129, 7168, 4)])
+def test_presplit_workspace_calls_equal_plain_calls_bitwise(N, K, M):
+    """b200_nvfp4_gemm_ws / gemv_multi_ws split the activation rows once into caller scratch; the
+    result must not differ from the plain calls in a single bit, also where the scratch cannot be
+    used (K = 16384: the image does not fit; K = 7168: CUDA-core path)."""
+    P = pkg()
+    W = dev_weight(host_triple((N, K), N + K + M))
+    x = torch.randn((M, K), device='cuda')
+    x[M - 1] *= 29.0
+    ws = P.split_workspace(M, K, x.device)
+    want = P.gemm(W, x)
+    got = torch.full_like(want, float('nan'))
+    P.gemm(W, x, got, ws=ws)
+    assert torch.equal(got, want)
+    if M <= 8:
+        W2 = dev_weight(host_triple((64, K), 7 + K))
+        ys = P.gemv_multi([W, W2], x, M)
+        ys_ws = [torch.full_like(y, float('nan')) for y in ys]
+        P.gemv_multi([W, W2], x, M, ys_ws, ws=ws)
+        for a, b in zip(ys, ys_ws): assert torch.equal(a, b)
+        assert torch.equal(ys[0], want)
+    assert (want != 0).float().mean() > 0.5
+    assert P.device_status() == 0
+
+
 def test_tensor_core_and_cuda_core_kernels_agree_within_tolerance(monkeypatch):
     """Not bit for bit (the tensor-core kernel rounds activations to 14 fractional bits of the
     row maximum, the CUDA-core kernels to fp16): both within the tolerance of the oracle, and of
