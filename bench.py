@@ -442,6 +442,15 @@ def main():
         m, b = bench_gemv_single(P, sub_steps, a.warmup, copies)
         sub['gemv_12288x4096_M1'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
                                       'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    if want('lm_head'):
+        N = 154880                                     # the vocabulary projection: 357 MB of weights, larger than L2 by itself
+        W, _ = make_weight(P, N, K_HID, 997)
+        xl = torch.randn((1, K_HID), device='cuda'); yl = torch.empty((1, N), device='cuda')
+        m = time_steps([lambda: P.gemm(W, xl, yl)], max(50, sub_steps // 10), a.warmup)
+        b = nv_bytes(N, K_HID) + K_HID * 4 + N * 4
+        sub['gemv_154880x4096_M1'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
+                                       'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+        del W
     if want('siblings'):
         for M in (2, 4, 8):
             m, b, _, _ = bench_siblings(P, M, sub_steps, a.warmup, copies)

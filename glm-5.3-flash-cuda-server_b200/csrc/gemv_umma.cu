@@ -586,12 +586,25 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
     p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = pre ? pre->stride : M; p.T = 1;
     p.dry_run = pre && pre->dry_run;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
+    {
+        // More tiles than SMs even at R = 128 (a vocabulary projection): several consecutive tiles per
+        // CTA, so that a CTA splits the activations and fills its pipeline once.  Same limits as the
+        // job-table launches; the results do not depend on T.
+        long tiles = 0;
+        for (int i = 0; i < g.n_jobs; ++i) tiles += (g.j[i].N + R - 1) / R;
+        const int nst = K / 256;
+        for (int T = 2; T * p.max_m <= 8; ++T) {
+            if (T * nst > UM_MAX_STEPS) break;
+            if ((size_t)T * R * (K / 16) + (size_t)nst * p.max_m * 1024 + 4 * (((size_t)R * 128 + 1023) & ~(size_t)1023) > 200 * 1024) break;
+            if (tiles / T >= nsm) p.T = T;
+        }
+    }
     int tasks = 0;
     for (int i = 0; i < g.n_jobs; ++i) {
         p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr,
                        pre ? pre->img + (size_t)pre->chunk * pre->chunk_bytes : nullptr,
                        pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0};
-        tasks += (g.j[i].N + R - 1) / R;
+        tasks += ((g.j[i].N + R - 1) / R + p.T - 1) / p.T;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
     }

@@ -178,11 +178,13 @@ def test_pipelined_and_general_kernels_agree_bitwise(monkeypatch):
 # ---- tensor-core kernel (K % 256 == 0, 16-byte aligned operands) ------------------------------------
 
 @pytest.mark.parametrize('N,K,M', [(512, 256, 1), (1000, 4096, 1), (4096, 1024, 3), (700, 1536, 8), (32, 4096, 1),
-                                   (64, 2048, 5), (300, 16384, 8), (300, 12288, 1), (20000, 512, 2), (129, 7168, 4)])
+                                   (64, 2048, 5), (300, 16384, 8), (300, 12288, 1), (20000, 512, 2), (129, 7168, 4),
+                                   (40000, 512, 1), (40000, 256, 3)])
 def test_tensor_core_gemv_vs_oracle_and_row_invariance(N, K, M):
     """Every shape class of the tensor-core kernel: several steps per stage (K up to 16384, where
     the activation rows are taken in chunks), swizzled and plain scale slabs (K/16 a multiple of
-    128 or not), row tiles of 8..128, more tiles than SMs.  Each row must also equal the
+    128 or not), row tiles of 8..128, more tiles than SMs (several tiles per CTA from twice the SM
+    count on).  Each row must also equal the
     single-row call bit for bit, whatever chunking or tile height the batched call used."""
     P, O = pkg(), oracle()
     t = host_triple((N, K), N + K + M)
