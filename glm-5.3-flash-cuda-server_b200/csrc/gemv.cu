@@ -235,19 +235,22 @@ template <int M, int MATH>
 static int launch_fast(const GemvParams& p, size_t smem, cudaStream_t s) {
     constexpr int R = RowsFor<M>::v;
     auto kern = k_gemv_nvfp4<M, R, MATH>;
-    static size_t smem_cfg = 0, occ_smem = (size_t)-1;     // one host thread at a time calls in
-    static int occ = 0;
-    if (smem > 48 * 1024 && smem > smem_cfg) {
+    struct PerDevice { size_t smem_cfg = 0, occ_smem = (size_t)-1; int occ = 0; };
+    static PerDevice cache[64];                      // the function attribute and the occupancy are per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    PerDevice& c = cache[dev];
+    if (smem > 48 * 1024 && smem > c.smem_cfg) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return launch_failed("gemv: cudaFuncSetAttribute");
-        smem_cfg = smem;
+        c.smem_cfg = smem;
     }
-    if (occ_smem != smem) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem) != cudaSuccess || occ < 1)
+    if (c.occ_smem != smem) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&c.occ, kern, GEMV_THREADS, smem) != cudaSuccess || c.occ < 1)
             return launch_failed("gemv: occupancy query");
-        occ_smem = smem;
+        c.occ_smem = smem;
     }
-    const int grid = std::min(p.total_tasks, sm_count() * occ);
+    const int grid = std::min(p.total_tasks, sm_count() * c.occ);
     kern<<<grid, GEMV_THREADS, smem, s>>>(p);
     return check_launch("k_gemv_nvfp4");
 }
@@ -286,7 +289,23 @@ int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s, 
     if (K <= 0 || (K & 15)) return B200_ESHAPE;
     GemvParams p{};
     p.n_jobs = n; p.K = K;
-    const size_t smem = (size_t)M * xs_chunks(K) * 16;
+    const size_t smem1 = (size_t)xs_chunks(K) * 16, smem = (size_t)M * smem1;
+    if (smem > 200 * 1024 && smem1 <= 200 * 1024 && M > 1) {
+        // The staged activations of all M rows do not fit shared memory: take the rows in chunks
+        // that do, so that which kernel computes a row never depends on M (a gemm row must equal
+        // the gemv of that row bit for bit).
+        const int mc = (int)(200 * 1024 / smem1);
+        for (int done = 0; done < M; done += mc) {
+            b200_gemv_job sub[B200_GEMV_MULTI_MAX];
+            for (int i = 0; i < n; ++i) {
+                sub[i] = jobs[i];
+                sub[i].y = jobs[i].y + (size_t)done * jobs[i].N;
+                sub[i].x = jobs[i].x + (size_t)done * K;
+            }
+            if (int rc = nvfp4_multi(sub, n, std::min(mc, M - done), K, s, nullptr)) return rc;
+        }
+        return B200_OK;
+    }
     bool fast = (K & 31) == 0 && smem <= 200 * 1024;
     int tasks = 0;
     const int tile = rows_per_tile(M);
@@ -394,7 +413,7 @@ extern "C" size_t b200_nvfp4_split_workspace_bytes(int M, int K) {
 extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, int M, int N, int K,
                                   int dtype, void* ws, b200_stream stream) {
     if (!W || M < 1) return B200_EINVAL;
-    if (!W->packed || !ws || M < 2) return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
+    if (!W->packed || !ws || M < 3 || !use_umma() || force_general()) return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
     if ((uintptr_t)ws & 255) return B200_EALIGN;
     // every row at once: one split launch, then one pass over the weights per 8 rows
     b200_gemv_job j{y, *W, x, N};

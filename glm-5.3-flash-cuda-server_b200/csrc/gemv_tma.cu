@@ -257,10 +257,12 @@ static int allow_big_smem(Kern kern, size_t need) {
 
 template <int NJ, int MATH>
 static int launch_tma_math(const GemvParams& p, const TmaCfg& cfg, size_t smem, int grid, cudaStream_t s) {
-    static bool ready = false;                      // one host thread at a time calls in
-    if (!ready) {
+    static bool ready_all[64] = {};                 // the attribute is per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!ready_all[dev]) {
         if (int rc = allow_big_smem(k_gemv_tma<NJ, MATH>, smem)) return rc;
-        ready = true;
+        ready_all[dev] = true;
     }
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid); lc.blockDim = dim3(GT_THREADS); lc.dynamicSmemBytes = smem; lc.stream = s;

@@ -581,7 +581,7 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
         for (int i = 0; i < g.n_jobs; ++i) tasks += (g.j[i].N + r - 1) / r;
         if (tasks <= nsm) { R = r; break; }
     }
-    static UmMaps maps;                              // one host thread at a time calls in
+    static thread_local UmMaps maps;                 // copied into the launch; one per host thread
     UmParams p{};
     p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = pre ? pre->stride : M; p.T = 1;
     p.dry_run = pre && pre->dry_run;
@@ -646,7 +646,8 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
 #endif
     if (p.dry_run) return B200_OK;
     const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
-    static bool ready[2] = {false, false};
+    static bool ready_all[64][2] = {};               // the attribute is per device
+    bool* ready = ready_all[dev >= 0 && dev < 64 ? dev : 0];
     if (!ready[gen]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) != cudaSuccess)
             return launch_failed("gemv_umma: cudaFuncSetAttribute");

@@ -228,6 +228,24 @@ def test_presplit_workspace_calls_equal_plain_calls_bitwise(N, K, M):
     assert P.device_status() == 0
 
 
+@pytest.mark.parametrize('N,K,M', [(300, 16384, 8), (1000, 4096, 5), (64, 12288, 8)])
+def test_cuda_core_fallback_row_invariance(monkeypatch, N, K, M):
+    """With the tensor-core kernel off, the CUDA-core kernels must keep the same invariant, also where
+    the staged activations of all M rows do not fit shared memory (the rows then go in chunks; the
+    kernel that computes a row must never depend on M)."""
+    monkeypatch.setenv('B200_NVFP4_UMMA', '0')
+    P, O = pkg(), oracle()
+    t_ = host_triple((N, K), N + K)
+    W = dev_weight(t_)
+    x = torch.randn((M, K), device='cuda')
+    y = P.gemm(W, x)
+    close(y.cpu().numpy(), O.gemm(x.cpu().numpy(), *t_))
+    for m in (0, M - 1):
+        assert torch.equal(P.gemm(W, x[m:m + 1].contiguous())[0], y[m]), m
+    ws = P.split_workspace(M, K, x.device)
+    assert torch.equal(P.gemm(W, x, ws=ws), y)       # the scratch variant follows the same switch
+
+
 def test_tensor_core_and_cuda_core_kernels_agree_within_tolerance(monkeypatch):
     """Not bit for bit (the tensor-core kernel rounds activations to 14 fractional bits of the
     row maximum, the CUDA-core kernels to fp16): both within the tolerance of the oracle, and of
