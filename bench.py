@@ -380,6 +380,38 @@ def cpu_siblings_step(host_sets, x):
     return outs
 
 
+def cpu_dequant(pk, sc, gs):
+    """reference ref/gen_moe.py:23-30: packed nibbles, e4m3 scales and the global scale to fp32 weights."""
+    KE2M1 = torch.tensor([0., .5, 1., 1.5, 2., 3., 4., 6.], dtype=torch.float32)
+    out_f, in_f = pk.shape[0], pk.shape[1] * 2
+    flat = pk.reshape(-1)
+    comb = torch.stack((flat & 0x0F, (flat >> 4) & 0x0F), dim=1).reshape(out_f, in_f).long()
+    vals = KE2M1[comb & 7] * torch.where((comb & 8).bool(), -1.0, 1.0)
+    return (vals.reshape(out_f, in_f // 16, 16) * (sc.float().reshape(out_f, in_f // 16, 1) / gs)).reshape(out_f, in_f)
+
+
+def cpu_moe_step(x, router, bias, experts, shared, topk, scale=2.5, limit=10.0):
+    """The MoE block as the reference's CPU path computes it (ref/gen_moe.py:62-96 restated): sigmoid
+    router with bias-ranked top-k, renormalised gates, clamped SwiGLU experts dequantised on the fly,
+    shared expert.  Returns y and the number of distinct routed experts."""
+    import torch.nn.functional as F
+    score = torch.sigmoid(F.linear(x, router))
+    sel = torch.topk(score + bias, topk, dim=-1).indices
+    w = score.gather(1, sel)
+    w = w / (w.sum(-1, keepdim=True) + 1e-20) * scale
+
+    def mlp(trip, rows):
+        g = torch.clamp(F.linear(rows, cpu_dequant(*trip[0])), max=limit)
+        u = torch.clamp(F.linear(rows, cpu_dequant(*trip[1])), -limit, limit)
+        return F.linear(F.silu(g) * u, cpu_dequant(*trip[2]))
+    y = mlp(shared, x)
+    distinct = torch.unique(sel).tolist()
+    for e in distinct:
+        tok, slot = (sel == e).nonzero(as_tuple=True)
+        y.index_add_(0, tok, mlp(experts[e], x[tok]) * w[tok, slot].unsqueeze(1))
+    return y, len(distinct)
+
+
 def cpu_baseline(P, state, max_seconds=20.0):
     sets, x = state[0], state[1]
     host = [(W.packed.cpu(), W.scale.cpu().view(torch.float8_e4m3fn), W.gscale.cpu()) for W in sets[0]]
@@ -501,6 +533,8 @@ def reference_arm(a, P, rank, peak):
     restated) on the host cores, on the headline workload."""
     if rank != 0:
         return
+    if a.gpus > 1:
+        return reference_arm_moe(a)
     O = G.load_oracle()
     rng = np.random.default_rng(1000)
     host = []
@@ -525,6 +559,44 @@ def reference_arm(a, P, rank, peak):
         'config': {'workload': 'six fused sibling NVFP4 gemvs sharing one input, K=4096, N=[4096,4096,4096,512,64,32], M=1 (configs[1])'},
         'cpu_baseline': {'value': v, 'unit': 'TB/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                          'sample': '%d full steps (bounded from --steps %d)' % (steps, a.steps)},
+        'e2e': {'value': v, 'unit': 'TB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }))
+
+
+def reference_arm_moe(a):
+    """N > 1: the metric is the expert-parallel MoE layer.  The reference has no multi-GPU form; its CPU
+    path for the same layer is the restated block above, on all host threads, on a bounded sample: 8
+    tokens through one layer (the GPU arm: --ep-tokens tokens through 3 layers).  Weights are random
+    NVFP4 bytes of the benchmark's shapes (drawing and quantising 435 real matrices on the CPU would
+    take minutes and does not change the time of a step)."""
+    H, I, E, topk, T = 4096, 1536, 144, 8, 8
+    gen = torch.Generator().manual_seed(50)
+
+    def trip(o, i):
+        pk = torch.randint(0, 256, (o, i // 2), dtype=torch.uint8, generator=gen)
+        sc = torch.randint(40, 72, (o, i // 16), dtype=torch.uint8, generator=gen).view(torch.float8_e4m3fn)   # scales around 0.1 .. 1.5
+        return pk, sc, torch.tensor([64.0])
+    experts = [(trip(I, H), trip(I, H), trip(H, I)) for _ in range(E)]
+    shared = (trip(I, H), trip(I, H), trip(H, I))
+    router = (torch.randn((E, H), generator=gen) * 0.02).to(torch.bfloat16).float()
+    bias = torch.randn(E, generator=gen) * 0.1
+    x = torch.randn((T, H), generator=gen)
+    steps, warm = max(1, min(a.steps, 3)), 1
+    cpu_moe_step(x, router, bias, experts, shared, topk)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        _, distinct = cpu_moe_step(x, router, bias, experts, shared, topk)
+    sec = (time.perf_counter() - t0) / steps
+    nbytes = (distinct + 1) * 3 * nv_bytes(I, H) + E * H * 2 + E * 4 + 2 * T * H * 4
+    v = nbytes / sec / 1e12
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'nvfp4_moe_ep_hbm_tbps', 'value': v, 'unit': 'TB/s', 'n_gpus': a.gpus,
+        'steps': steps, 'warmup': warm, 'ms_per_step': sec * 1e3, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': 'MoE layer on the host cores: 144 experts, top-8 + shared expert, hidden 4096, inter 1536 (configs[4] has no multi-GPU reference: its CPU path on one layer)'},
+        'tokens_per_s': T / sec,
+        'cpu_baseline': {'value': v, 'unit': 'TB/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': '%d tokens through one layer, %d distinct routed experts; %d steps' % (T, distinct, steps)},
         'e2e': {'value': v, 'unit': 'TB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
     }))
 
