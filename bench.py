@@ -4,15 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
 
 Headline (N = 1): the six fused sibling gemvs that share one input (K = 4096, outputs 4096, 4096,
-4096, 512, 64, 32; all NVFP4, M = 1) -- one launch of k_gemv_nvfp4 per step.  `value` is the
+4096, 512, 64, 32; all NVFP4, M = 1) -- one launch of the tensor-core kernel k_gemv_umma per step.  `value` is the
 achieved HBM rate in TB/s: algorithmic bytes of one step / device time of one step, inputs
 resident in HBM, the step rotating over weight copies whose total exceeds L2 several times.
 `e2e` is the same step through the C ABI with HOST buffers: the activation row is copied from
 pinned host memory and the six outputs are copied back inside the timed region (weights are
 model state and stay resident, as they do in the engine that calls this path).
-`sub` carries the other single-GPU configurations (single gemv [12288x4096]; siblings at
-M = 2, 4, 8; MoE decode layer at M = 1 and 4 with microseconds per layer; quantiser), each with
-its own byte count and fraction of the measured HBM peak.
+`sub` carries the other single-GPU configurations (single gemv [12288x4096]; the vocabulary
+projection; siblings at M = 2, 4, 8; the same matrix against 32 and 128 rows; MoE layer at 1, 4, 8
+and 64 tokens with microseconds per layer; quantiser), each with its own byte count and fraction of
+the measured HBM peak.
+N > 1 (torchrun, one rank per GPU): the headline path does not shard, so every rank runs the
+headline workload on its own GPU (value = sum over GPUs over the slowest rank's time, weak scaling);
+the expert-parallel MoE layer, the one part with a real exchange, is reported as `ep_moe`.
 All data is synthetic: seeded N(0, 0.02) bf16 weights quantised by this library's bit-exact
 quantiser, N(0, 1) fp32 activations.
 """
