@@ -56,6 +56,9 @@ def lib():
         L.b200_nvfp4_split_workspace_bytes.restype = st; L.b200_nvfp4_split_workspace_bytes.argtypes = [ci, ci]
         L.b200_nvfp4_gemm_ws.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp, vp]
         L.b200_nvfp4_gemv_multi_ws.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp, vp]
+        L.b200_nvfp4_gemm_bf16_workspace_bytes.restype = st; L.b200_nvfp4_gemm_bf16_workspace_bytes.argtypes = [ci, ci]
+        L.b200_nvfp4_gemm_bf16.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, vp, vp]
+        L.b200_nvfp4_quantize_tokens.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
         L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
         L.b200_bf16_to_f32.argtypes = [vp, vp, st, vp]
         L.b200_nvfp4_quantize.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
@@ -74,7 +77,7 @@ def lib():
 
 ENOTIMPL = 6
 EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
-           'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
+           'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
            'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release']
 
@@ -92,6 +95,7 @@ def device_status(clear=False):
 
 
 OPT_STABLE_WEIGHTS = 1
+OPT_PREFILL_FP4 = 2
 
 
 def set_option(option, value):
@@ -151,6 +155,36 @@ def gemm(W, x, y=None, dtype=BF16, stream=None, ws=None):
     else:
         check(lib().b200_nvfp4_gemm(_ptr(y), C.byref(ref), _ptr(x2), M, N, K, dtype, stream_ptr(stream)), 'b200_nvfp4_gemm')
     return y if x.dim() == 2 else y[0]
+
+
+def gemm_bf16_workspace(M, K, device):
+    return torch.empty(lib().b200_nvfp4_gemm_bf16_workspace_bytes(M, K), dtype=torch.uint8, device=device)
+
+
+def gemm_bf16(W, x_bf16, y=None, ws=None, stream=None):
+    """The wide GEMM: y[M,N] f32 = x[M,K] bf16 . W^T with the activations quantised to NVFP4 per token."""
+    M, K = x_bf16.shape
+    assert W.K == K and x_bf16.dtype == torch.bfloat16
+    if y is None:
+        y = torch.empty((M, W.N), dtype=torch.float32, device=x_bf16.device)
+    if ws is None:
+        ws = gemm_bf16_workspace(M, K, x_bf16.device)
+    ref = W.wref()
+    check(lib().b200_nvfp4_gemm_bf16(_ptr(y), C.byref(ref), _ptr(x_bf16), M, W.N, K, _ptr(ws), stream_ptr(stream)), 'b200_nvfp4_gemm_bf16')
+    return y
+
+
+def quantize_tokens(x, stream=None):
+    """Per-token NVFP4 quantisation of x [M,K] (bf16 or f32): packed [M,K/2], scale [M,K/16] (returned
+    row-major; the library writes it step-major), gs [M]."""
+    M, K = x.shape
+    dev = x.device
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    sfb = torch.empty((K // 256, M, 16), dtype=torch.uint8, device=dev)
+    gs = torch.empty(M, dtype=torch.float32, device=dev)
+    check(lib().b200_nvfp4_quantize_tokens(_ptr(x), 1 if x.dtype == torch.float32 else 0, M, K, _ptr(packed), _ptr(sfb), _ptr(gs),
+                                           stream_ptr(stream)), 'b200_nvfp4_quantize_tokens')
+    return packed, sfb.permute(1, 0, 2).reshape(M, K // 16).contiguous(), gs
 
 
 def gemv(W, x, y=None, stream=None):

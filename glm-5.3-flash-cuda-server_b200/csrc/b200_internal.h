@@ -17,6 +17,9 @@ int launch_failed(const char* what);
 unsigned int* device_status_ptr();
 // 1 if the caller declared weight buffers immutable while kernels run (B200_OPT_STABLE_WEIGHTS).
 int stable_weights_option();
+// 1 if calls with scratch and >= 16 activation rows may quantise the activations to NVFP4 (B200_OPT_PREFILL_FP4).
+int prefill_fp4_option();
+constexpr int PREFILL_MIN_ROWS = 16;
 
 // One launch's worth of NVFP4 gemv jobs as the kernels see them.  task0 is the index of the
 // job's first row tile in the launch's flat tile list (general kernel only).
@@ -28,6 +31,12 @@ struct GemvParams {
     GemvJobDev j[B200_GEMV_MULTI_MAX];
     int n_jobs, total_tasks, K;
 };
+
+// tmap.cu: TMA tensor map of a u8 matrix [rows, row_bytes] with box [box_bytes x box_rows] (128B-swizzled or
+// plain), written to `out` (128 bytes, host memory).  cached: remember the encoded map (weights).
+bool tmap_available();
+bool tmap_u8_2d(void* out, const void* base, size_t rows, size_t row_bytes, int box_bytes, int box_rows, bool swz, bool cached);
+bool scale_box(int K, int* box, int* swz);
 
 // gemv.cu
 int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s, void* split_ws);
@@ -61,5 +70,18 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
                      void* scratch, int M, cudaStream_t s, bool planned);
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
 int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s);
+
+// gemm_mxf4.cu: the wide GEMM with both operands in NVFP4 (activations quantised per token first).
+// One job: `rows` activation rows, starting at row `row0` of the quantised activation buffer, against one
+// weight matrix of N rows; y[m * ldy + n].  gs_x points at the job's first per-token global scale.
+// mw, ms: tensor maps of the weight in GLOBAL memory (table launches; box height = the launch's R).
+struct GxJob { float* y; const float* gs_w; const float* gs_x; const void* mw; const void* ms; int row0; int rows; int N; int ldy; };
+size_t gemm_mxf4_ws_bytes(int M, int K);
+bool gemm_mxf4_shape_ok(int K);
+int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s);
+int quant_act_launch(int mode, const void* x, const void* x2, float limit, const int* src_row, const int* m_dev, int M,
+                     int rows_launch, int K, unsigned char* xq, unsigned char* sfb, size_t sfb_rows, float* gsx, cudaStream_t s);
+int gemm_mxf4_table(const GxJob* table, int max_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
+                    const unsigned char* sfb, size_t sfb_rows, cudaStream_t s);
 
 }  // namespace b200

@@ -43,6 +43,17 @@ int stable_weights_option() {
 }
 void set_stable_weights(int v) { g_stable_weights = v ? 1 : 0; }
 
+// 1 (default): calls that carry scratch and 16 or more activation rows take the wide tensor-core GEMM,
+// which quantises the activations to NVFP4; 0: every call keeps fp32-activation accuracy.
+static int g_prefill_fp4 = -1;
+int prefill_fp4_option() {
+    if (g_prefill_fp4 < 0) {
+        const char* e = getenv("B200_PREFILL_FP4");
+        g_prefill_fp4 = (e && *e == '0') ? 0 : 1;
+    }
+    return g_prefill_fp4;
+}
+
 int launch_failed(const char* what) {
     const cudaError_t e = cudaGetLastError();
     fprintf(stderr, "b200_nvfp4: %s failed: %s\n", what, cudaGetErrorString(e));
@@ -74,9 +85,9 @@ extern "C" const char* b200_nvfp4_strerror(int code) {
 extern "C" int b200_nvfp4_version(void) { return 100; }
 
 extern "C" int b200_nvfp4_set_option(int option, int value) {
-    if (option != B200_OPT_STABLE_WEIGHTS) return B200_EINVAL;
-    b200::set_stable_weights(value);
-    return B200_OK;
+    if (option == B200_OPT_STABLE_WEIGHTS) { b200::set_stable_weights(value); return B200_OK; }
+    if (option == B200_OPT_PREFILL_FP4) { b200::g_prefill_fp4 = value ? 1 : 0; return B200_OK; }
+    return B200_EINVAL;
 }
 
 extern "C" int b200_nvfp4_device_status(unsigned int* out, int clear) {

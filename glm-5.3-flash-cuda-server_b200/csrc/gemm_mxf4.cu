@@ -1,0 +1,524 @@
+// gemm_mxf4.cu -- the wide (prefill / batched, M >= 16) NVFP4 GEMM: y[M,N] = x[M,K] . W[N,K]^T on
+// tcgen05.mma kind::mxf4nvf4.block_scale.block16 with BOTH operands in NVFP4.
+//
+// The weights are used exactly as the format stores them (packed e2m1 bytes and e4m3 block
+// scales, read through TMA).  The activations are quantised to NVFP4 first, one token at a time,
+// by k_quant_act: the reference's own quant_block rule (tools/requant_dense_nvfp4.py:53-68) with a
+// per-token global scale 2688 / amax(token), so that a token's result never depends on the rest of
+// its batch.  That costs about 9 % per-element activation error; results are therefore judged against
+// deq(W) . deq(quant(x)), and the library keeps the exact small-batch kernels (gemv_umma.cu) for
+// callers that want fp32-activation accuracy.  The reference streams W once per chunk of 4 rows
+// (kernels/gemv.cu:369-396); here W is read ONCE for up to 256 rows.
+//
+// One CTA per (tile of R <= 128 weight rows, job of up to NT activation rows); K walked in steps of
+// 256.  The accumulator D[128 weight rows (lanes), NT tokens (columns)] stays in TMEM for the whole K.
+//   warp 0      TMA producer: the tile's weight scale rows once (slabs [R x 128 B]); per step one
+//               128B-swizzled box of packed weights [128 B x R], one of packed activations
+//               [128 B x NT] and the step's activation scales (one contiguous NT x 16 B chunk: the
+//               quantiser writes them step-major) into a ring of stages.  Lane l issues steps l, l+32, ..
+//   warp 1      MMA issuer: four tcgen05.mma (K = 64 each, N = NT) per step, tcgen05.commit frees the stage
+//   warp 2      allocates / frees TMEM
+//   warps 4-11  two groups of four warps (one per TMEM lane quadrant) on alternate steps move the
+//               step's scales into TMEM with tcgen05.st (lane r % 32, column r / 32: the layout the
+//               block-scaled MMA reads): 16 columns for the weights' 128 x 16 scale bytes, NT/8 for the
+//               activations'.  Afterwards each group reads half of the accumulator columns, applies
+//               1 / (gs_w * gs_x[token]) and writes y (lanes = consecutive n: coalesced).
+// Barriers full/sf/empty are per step and used once (K <= 16384: at most 64 steps).  Every wait is
+// bounded (tma_pipe.cuh).  No cluster launch, no multicast.
+#include "b200_internal.h"
+#include "quant_core.cuh"
+#include "tma_pipe.cuh"
+#include <cuda.h>
+#include <cstdio>
+
+namespace b200 {
+
+constexpr int GX_THREADS = 384;
+constexpr int GX_MOVERS = 256;
+constexpr int GX_MAX_STEPS = 64;                   // K <= 16384
+constexpr int GX_MAX_STAGES = 8;
+constexpr int GX_TMEM_COLS = 512;                  // accumulator [0, NT) | scale slots from column 256
+constexpr int GX_COL_SF = 256;
+constexpr uint32_t GX_A_BYTES = 16384;             // the MMA always reads 128 rows x 128 B of a stage
+
+struct GxParams {
+    const GxJob* table;                            // jobs in global memory (written by an earlier kernel), or nullptr:
+    GxJob one;                                     // ... job j = activation rows [j * NT, j * NT + NT) of `one`
+    const unsigned char* sfb;                      // activation scales [K/256][sfb_rows][16]
+    size_t sfb_rows;
+    unsigned int* status;
+    int n_jobs, K, R, stages, prefetch_before_wait;
+    int sc_box, sc_swz;
+};
+
+__device__ __forceinline__ void gx_tma_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t gx_desc(uint32_t saddr) {
+    // K-major operand tile, 128B-swizzled: start address >> 4 | SBO = 1024 B (8 rows) | version 1 | SWIZZLE_128B
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(1024u >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void gx_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void gx_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void gx_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+// tcgen05.st of 4*CB registers (32x32b): register i goes to column i of the warp's lane quadrant.
+template <int N> struct GxSt;
+template <> struct GxSt<4> {
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t* r) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
+                     :: "r"(a), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+    }
+};
+template <> struct GxSt<8> {
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t* r) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     :: "r"(a), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+    }
+};
+template <> struct GxSt<16> {
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t* r) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                     :: "r"(a), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+    }
+};
+template <> struct GxSt<32> {
+    static __device__ __forceinline__ void st(uint32_t a, const uint32_t* r) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                     "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                     :: "r"(a), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+    }
+};
+
+template <int NT>
+__global__ void __launch_bounds__(GX_THREADS, 1)
+k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensorMap map_x,
+            const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s) {
+    constexpr int CB = NT / 32;                    // TMEM columns the activation scales of one 64-k block fill
+    constexpr int CBS = CB < 4 ? 4 : CB;           // ... and the columns between two blocks (scale addresses stay multiples of 4)
+    constexpr int SLOT = 16 + 4 * CBS;             // TMEM columns of one step's scales
+    constexpr uint32_t AB_BYTES = GX_A_BYTES + NT * 128u;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint64_t full_bar[GX_MAX_STEPS], sf_bar[GX_MAX_STEPS], empty_bar[GX_MAX_STEPS], done_bar, sc_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ float sx[NT];                       // 1 / (gs_w * gs_x[token]) of the job's rows
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = p.K, nst = K >> 8, R = p.R;
+
+    GxJob J;
+    const int tile_n = (int)blockIdx.x / p.n_jobs, ji = (int)blockIdx.x - tile_n * p.n_jobs;
+    const void* mw = &map_w;
+    const void* ms = &map_s;
+    if (p.table) {
+        pdl_wait();                                // the table is written by an earlier kernel of the stream
+        J = p.table[ji];
+        if (J.rows <= 0) return;                   // an unused slot: the whole CTA leaves before it owns anything
+        mw = J.mw; ms = J.ms;
+    } else {
+        J = p.one;
+        J.row0 = ji * NT;
+        J.rows = min(NT, J.rows - J.row0);
+        J.y += (size_t)J.row0 * J.ldy;
+        J.gs_x += J.row0;
+    }
+    const int rown0 = tile_n * R;                  // first weight row of the tile
+    if (rown0 >= J.N) return;
+
+    unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+    unsigned char* scl = ring + (size_t)p.stages * AB_BYTES;                    // the tile's weight scale rows: slabs [R x sc_box], 1 KB aligned (swizzle)
+    unsigned char* sfbs = scl + (size_t)R * (K >> 4);                           // per stage NT x 16 B of activation scales
+
+    pdl_launch_dependents();
+    if (warp >= 4) {
+        const int i = tid - 128;
+        if (i < nst) mbar_init(smem_u32(&full_bar[i]), 1);
+        else if (i >= 64 && i < 64 + nst) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
+        else if (i >= 128 && i < 128 + nst) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
+        else if (i == 192) mbar_init(smem_u32(&done_bar), 1);
+        else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
+        mbar_fence_init();
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_base_s)), "r"(GX_TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    gx_fence_before();
+    __syncthreads();
+    gx_fence_after();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" :: "l"(mw) : "memory");
+            asm volatile("prefetch.tensormap [%0];" :: "l"(ms) : "memory");
+            asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+        }
+        if (!p.prefetch_before_wait) pdl_wait();
+        const int nslab = (K >> 4) / p.sc_box;
+        if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), (uint32_t)R * (uint32_t)(K >> 4));
+        __syncwarp();
+        for (int q = lane; q < nslab; q += 32)
+            gx_tma_2d(smem_u32(scl) + (uint32_t)q * (uint32_t)R * (uint32_t)p.sc_box, ms, q * p.sc_box, rown0, smem_u32(&sc_bar));
+        const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+        const uint32_t step_bytes = (uint32_t)R * 128u + NT * 128u + NT * 16u;
+        for (int g = lane; g < nst; g += 32) {
+            const int s = g % p.stages;
+            if (g >= p.stages) mbar_wait_spin(empty0 + (g - p.stages) * 8, 0, p.status, 9);
+            const uint32_t bar = full0 + g * 8, dst = smem_u32(ring) + (uint32_t)s * AB_BYTES;
+            mbar_expect_tx(bar, step_bytes);
+            gx_tma_2d(dst, mw, g * 128, rown0, bar);                              // weights may be read early (stable weights)
+            pdl_wait();                                                           // the activations come from the quantiser launch
+            gx_tma_2d(dst + GX_A_BYTES, &map_x, g * 128, J.row0, bar);
+            bulk_g2s(smem_u32(sfbs) + (uint32_t)s * NT * 16u, p.sfb + ((size_t)g * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
+        }
+        __syncwarp();
+        // The tcgen05.commit arrivals on empty_bar are asynchronous: wait for the last one of every
+        // stage, or the CTA could exit with an arrival in flight that lands in the next CTA's shared memory.
+        for (int g = max(0, nst - p.stages) + lane; g < nst; g += 32)
+            mbar_wait_spin(empty0 + g * 8, 0, p.status, 10);
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer: the whole warp walks the loop, lane 0 issues ----
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
+        const uint64_t dA0 = gx_desc(smem_u32(ring)), dB0 = gx_desc(smem_u32(ring) + GX_A_BYTES);
+        const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+        int s = 0;
+        for (int g = 0; g < nst; ++g) {
+            mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
+            gx_fence_after();
+            if (lane == 0) {
+                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)s * SLOT;
+                const uint64_t so = (uint64_t)(((uint32_t)s * AB_BYTES) >> 4);
+                #pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                 " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+                                 :: "r"(tmem), "l"(dA0 + so + kb * 2), "l"(dB0 + so + kb * 2), "r"(idesc), "r"((uint32_t)((g | kb) != 0)),
+                                    "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
+                }
+                gx_commit(empty0 + g * 8);
+            }
+            __syncwarp();
+            if (++s == p.stages) s = 0;
+        }
+        if (lane == 0) gx_commit(smem_u32(&done_bar));
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ---- scale movers, then epilogue ----
+        const int t = tid - 128, grp = t >> 7, q4 = warp & 3;
+        const uint32_t tq = tmem + ((uint32_t)(q4 * 32) << 16);
+        pdl_wait();
+        if (t < NT) sx[t] = t < J.rows ? 1.0f / (J.gs_w[0] * J.gs_x[t]) : 0.f;
+        named_sync(1, GX_MOVERS);
+        const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
+        mbar_wait_spin(smem_u32(&sc_bar), 0, p.status, 12);
+        const int valid = J.N - rown0;               // weight rows of this tile that exist (may exceed R)
+        int s = grp % p.stages;
+        for (int g = grp; g < nst; g += 2) {
+            mbar_wait_spin(full0 + g * 8, 0, p.status, 13);
+            // weights: lane l holds rows l, l+32, l+64, l+96, 16 bytes each = four 64-k blocks x four scales;
+            // block kb of row 32c + l goes to column kb*4 + c
+            uint32_t ra[16];
+            #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int r = lane + 32 * c;
+                uint32_t off;
+                if (p.sc_swz) off = (uint32_t)(g >> 3) * (uint32_t)R * 128u + (uint32_t)r * 128u + (uint32_t)(((g & 7) ^ (r & 7)) << 4);
+                else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)g * 16u;
+                const uint4 v = (r < R && r < valid) ? *reinterpret_cast<const uint4*>(scl + off) : make_uint4(0u, 0u, 0u, 0u);
+                ra[c] = v.x; ra[4 + c] = v.y; ra[8 + c] = v.z; ra[12 + c] = v.w;
+            }
+            // activations: lane l holds tokens l, l+32, ..; block kb of token 32c + l goes to column 16 + kb*CBS + c
+            uint32_t rb[4 * CBS];
+            const unsigned char* sb = sfbs + (size_t)s * NT * 16;
+            #pragma unroll
+            for (int c = 0; c < CBS; ++c) {
+                const uint4 v = c < CB ? *reinterpret_cast<const uint4*>(sb + (size_t)(lane + 32 * c) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                rb[c] = v.x; rb[CBS + c] = v.y; rb[2 * CBS + c] = v.z; rb[3 * CBS + c] = v.w;
+            }
+            const uint32_t slot = tq + GX_COL_SF + (uint32_t)s * SLOT;
+            GxSt<16>::st(slot, ra);
+            GxSt<4 * CBS>::st(slot + 16, rb);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            gx_fence_before();
+            mbar_arrive(sf0 + g * 8);
+            s += 2; while (s >= p.stages) s -= p.stages;
+        }
+        // epilogue: group grp takes columns [grp * NT/2, (grp + 1) * NT/2)
+        mbar_wait_spin(smem_u32(&done_bar), 0, p.status, 14);
+        gx_fence_after();
+        const int r = q4 * 32 + lane, row = rown0 + r;
+        const bool ok = r < R && row < J.N;
+        #pragma unroll 1
+        for (int c0 = grp * (NT / 2); c0 < (grp + 1) * (NT / 2); c0 += 16) {
+            if (c0 >= J.rows) break;                 // warp-uniform: the remaining tokens do not exist
+            uint32_t d[16];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
+                           "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+                         : "r"(tq + (uint32_t)c0));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (ok) {
+                #pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + j < J.rows) J.y[(size_t)(c0 + j) * J.ldy + row] = __uint_as_float(d[j]) * sx[c0 + j];
+            }
+        }
+    }
+    gx_fence_before();
+    __syncthreads();
+    if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(GX_TMEM_COLS));
+}
+
+// ---- per-token activation quantiser -------------------------------------------------------------
+// One CTA per activation row.  MODE 0: bf16 rows; 1: f32 rows; 2: f32 rows of the clamped SwiGLU
+// silu(min(g, limit)) * clamp(u, -limit, limit) of two product vectors (the MoE down projection's input).
+// src_row != nullptr: output row r is input row src_row[r] (gathers token rows into expert order).
+// Output: packed [*, K/2] codes, scales step-major [K/256][sfb_rows][16], gsx[r] = 2688 / amax(row r).
+// Rows in [M, rows_total) only get zero scales (they pad the last tile of a dense call).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+k_quant_act(const void* __restrict__ xin, const void* __restrict__ xin2, float limit, const int* __restrict__ src_row,
+            const int* __restrict__ m_dev, int M, int K, unsigned char* __restrict__ xq, unsigned char* __restrict__ sfb,
+            size_t sfb_rows, float* __restrict__ gsx) {
+    __shared__ float red[8];
+    const int row = blockIdx.x, tid = threadIdx.x, groups = K >> 4;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (m_dev) M = m_dev[0];                        // row count decided on the device (rows grouped by expert)
+    if (row >= M) {
+        if (m_dev) return;
+        for (int st = tid; st < (K >> 8); st += 256)
+            *reinterpret_cast<uint4*>(sfb + ((size_t)st * sfb_rows + row) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const size_t src = src_row ? (size_t)src_row[row] : (size_t)row;
+    auto load = [&](int g, float (&v)[16]) {
+        if (MODE == 0) {
+            const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + src * K) + 2 * g;
+            const uint4 a = r[0], b = r[1];
+            const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) { v[2 * j] = __uint_as_float(u[j] << 16); v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+        } else {
+            const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(xin) + src * K) + 4 * g;
+            const float4* r2 = MODE == 2 ? reinterpret_cast<const float4*>(static_cast<const float*>(xin2) + src * K) + 4 * g : nullptr;
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 a = r[q];
+                if (MODE == 2) {
+                    const float4 u = r2[q];
+                    const float gg[4] = {fminf(a.x, limit), fminf(a.y, limit), fminf(a.z, limit), fminf(a.w, limit)};
+                    const float uu[4] = {fminf(fmaxf(u.x, -limit), limit), fminf(fmaxf(u.y, -limit), limit),
+                                         fminf(fmaxf(u.z, -limit), limit), fminf(fmaxf(u.w, -limit), limit)};
+                    a = make_float4((gg[0] / (1.f + __expf(-gg[0]))) * uu[0], (gg[1] / (1.f + __expf(-gg[1]))) * uu[1],
+                                    (gg[2] / (1.f + __expf(-gg[2]))) * uu[2], (gg[3] / (1.f + __expf(-gg[3]))) * uu[3]);
+                }
+                v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+            }
+        }
+    };
+    float first[16];
+    float a = 0.f;
+    for (int g = tid; g < groups; g += 256) {
+        float v[16];
+        load(g, v);
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) { a = fmaxf(a, fabsf(v[j])); if (g == tid) first[j] = v[j]; }
+    }
+    a = warp_max(a);
+    if ((tid & 31) == 0) red[tid >> 5] = a;
+    __syncthreads();
+    a = red[0];
+    #pragma unroll
+    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+    const float gs = nvfp4_global_scale(a);
+    if (tid == 0) gsx[row] = gs;
+    for (int g = tid; g < groups; g += 256) {
+        float v[16];
+        if (g == tid) {
+            #pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = first[j];
+        } else load(g, v);
+        uint32_t lo, hi; int code;
+        quantize_group(v, gs, lo, hi, code);
+        reinterpret_cast<uint2*>(xq + (size_t)row * (K >> 1))[g] = make_uint2(lo, hi);
+        sfb[((size_t)(g >> 4) * sfb_rows + row) * 16 + (g & 15)] = (unsigned char)code;
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+size_t gemm_mxf4_ws_bytes(int M, int K) {
+    if (M < 1 || K < 256) return 256;
+    const size_t rows = ((size_t)M + 255) / 256 * 256;
+    return up256(rows * (size_t)(K / 2)) + up256(rows * (size_t)(K / 16)) + up256(rows * 4);
+}
+
+bool gemm_mxf4_shape_ok(int K) {
+    int b, z;
+    return !(K & 255) && K >= 256 && K <= 16384 && scale_box(K, &b, &z) && tmap_available();
+}
+
+int quant_act_launch(int mode, const void* x, const void* x2, float limit, const int* src_row, const int* m_dev, int M,
+                     int rows_launch, int K, unsigned char* xq, unsigned char* sfb, size_t sfb_rows, float* gsx, cudaStream_t s) {
+    if (rows_launch < 1) return B200_OK;
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(rows_launch); lc.blockDim = dim3(256); lc.dynamicSmemBytes = 0; lc.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+    cudaError_t e;
+    if (mode == 0) e = cudaLaunchKernelEx(&lc, k_quant_act<0>, x, x2, limit, src_row, m_dev, M, K, xq, sfb, sfb_rows, gsx);
+    else if (mode == 1) e = cudaLaunchKernelEx(&lc, k_quant_act<1>, x, x2, limit, src_row, m_dev, M, K, xq, sfb, sfb_rows, gsx);
+    else e = cudaLaunchKernelEx(&lc, k_quant_act<2>, x, x2, limit, src_row, m_dev, M, K, xq, sfb, sfb_rows, gsx);
+    if (e != cudaSuccess) return launch_failed("k_quant_act");
+    return check_launch("k_quant_act");
+}
+
+// Shared memory and stage count of a launch; false if not even two stages fit.
+template <int NT>
+static int gx_launch_t(GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& ms, int grid, cudaStream_t s) {
+    auto kern = k_gemm_mxf4<NT>;
+    static int attr_cache[64][2] = {};               // [device] = {optin, static bytes + 1}
+    static bool ready[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return launch_failed("gemm_mxf4: cudaGetDevice");
+    if (dev < 0 || dev >= 64) dev = 0;
+    int* ac = attr_cache[dev];
+    if (!ac[1]) {
+        cudaFuncAttributes fa;
+        int oi = 0;
+        if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
+            cudaDeviceGetAttribute(&oi, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemm_mxf4: attributes");
+        ac[0] = oi; ac[1] = (int)fa.sharedSizeBytes + 1;
+    }
+    const size_t static_smem = (size_t)ac[1] - 1;
+    const size_t room = (size_t)ac[0] - static_smem - 2048;        // 1 KB alignment slack + 1 KB system reserve
+    const size_t fixed = (size_t)p.R * (p.K / 16);
+    const size_t per_stage = GX_A_BYTES + (size_t)NT * 128 + (size_t)NT * 16;
+    if (fixed + 2 * per_stage > room) return B200_ENOTIMPL;
+    const int nst = p.K / 256;
+    int stages = (int)std::min<size_t>((room - fixed) / per_stage, (size_t)GX_MAX_STAGES);
+    stages = std::min(stages, (GX_TMEM_COLS - GX_COL_SF) / (16 + 4 * std::max(NT / 32, 4)));
+    stages = std::min(stages, nst);
+    if (stages < 2 && stages < nst) return B200_ENOTIMPL;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * per_stage + fixed + 1024;
+    if (!ready[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ac[0] - static_smem)) != cudaSuccess)
+            return launch_failed("gemm_mxf4: cudaFuncSetAttribute");
+        ready[dev] = true;
+    }
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(grid); lc.blockDim = dim3(GX_THREADS); lc.dynamicSmemBytes = smem; lc.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+    if (cudaLaunchKernelEx(&lc, kern, p, mx, mw, ms) != cudaSuccess) return launch_failed("k_gemm_mxf4");
+    return check_launch("k_gemm_mxf4");
+}
+
+static int gx_launch(int NT, GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& ms, int grid, cudaStream_t s) {
+    switch (NT) {
+        case 32: return gx_launch_t<32>(p, mx, mw, ms, grid, s);
+        case 64: return gx_launch_t<64>(p, mx, mw, ms, grid, s);
+        case 128: return gx_launch_t<128>(p, mx, mw, ms, grid, s);
+        default: return gx_launch_t<256>(p, mx, mw, ms, grid, s);
+    }
+}
+
+// Token tile for M activation rows against N weight rows: as narrow as covers M up to 128; beyond
+// that 256 columns per CTA unless the narrower tile still fits one wave of CTAs.
+static int pick_nt(int M, int N) {
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128) return 128;
+    const int tiles_n = (N + 127) / 128, nsm = sm_count();
+    return tiles_n * ((M + 127) / 128) <= nsm ? 128 : 256;
+}
+
+// Dense: y[M, N] = quant(x)[M, K] . W^T.  x_kind 0: bf16, 1: f32.  ws: gemm_mxf4_ws_bytes(M, K).
+int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s) {
+    if (!y || !W || !W->packed || !W->scale || !W->gscale || !x || !ws || M < 1 || N < 1) return B200_EINVAL;
+    if (!gemm_mxf4_shape_ok(K)) return B200_ENOTIMPL;
+    if (((uintptr_t)W->packed & 15) || ((uintptr_t)W->scale & 15) || ((uintptr_t)x & 15) || ((uintptr_t)ws & 255)) return B200_ENOTIMPL;
+    const int NT = pick_nt(M, N), n_jobs = (M + NT - 1) / NT, nsm = sm_count();
+    // weight rows per CTA: with one token tile the kernel is bandwidth-bound and wants every SM busy (the
+    // smallest multiple of 8 whose tiles still fit the SMs); with several, the MMA is always 128 rows tall.
+    int R = 128;
+    if (n_jobs == 1)
+        for (int r = 8; r <= 128; r += 8) if ((N + r - 1) / r <= nsm) { R = r; break; }
+    const size_t rows = ((size_t)M + 255) / 256 * 256;
+    unsigned char* xq = static_cast<unsigned char*>(ws);
+    unsigned char* sfb = xq + up256(rows * (size_t)(K / 2));
+    float* gsx = reinterpret_cast<float*>(sfb + up256(rows * (size_t)(K / 16)));
+    GxParams p{};
+    p.table = nullptr;
+    p.one = GxJob{y, W->gscale, gsx, nullptr, nullptr, 0, M, N, N};
+    p.sfb = sfb; p.sfb_rows = rows;
+    p.status = device_status_ptr();
+    if (!p.status) return B200_ENOTIMPL;
+    p.n_jobs = n_jobs; p.K = K; p.R = R; p.prefetch_before_wait = stable_weights_option();
+    if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
+    CUtensorMap mx, mw, ms;
+    if (!tmap_u8_2d(&mw, W->packed, (size_t)N, (size_t)K / 2, 128, R, true, true) ||
+        !tmap_u8_2d(&ms, W->scale, (size_t)N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0, true) ||
+        !tmap_u8_2d(&mx, xq, (size_t)M, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
+    if (int rc = quant_act_launch(x_kind ? 1 : 0, x, nullptr, 0.f, nullptr, nullptr, M, n_jobs * NT, K, xq, sfb, rows, gsx, s)) return rc;
+    const int tiles_n = (N + R - 1) / R;
+    return gx_launch(NT, p, mx, mw, ms, tiles_n * n_jobs, s);
+}
+
+// Jobs from a table in device memory (rows grouped by expert).  Every job's weight maps were encoded
+// with box height R and N weight rows; the activation rows of all jobs live in one quantised buffer
+// (xq [x_rows, K/2], scales sfb [K/256][sfb_rows][16]).
+int gemm_mxf4_table(const GxJob* table, int max_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
+                    const unsigned char* sfb, size_t sfb_rows, cudaStream_t s) {
+    if (!gemm_mxf4_shape_ok(K)) return B200_ENOTIMPL;
+    GxParams p{};
+    p.table = table;
+    p.sfb = sfb; p.sfb_rows = sfb_rows;
+    p.status = device_status_ptr();
+    if (!p.status) return B200_ENOTIMPL;
+    p.n_jobs = max_jobs; p.K = K; p.R = R; p.prefetch_before_wait = 0;
+    if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
+    CUtensorMap mx;
+    if (!tmap_u8_2d(&mx, xq, x_rows, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
+    const int tiles_n = (N + R - 1) / R;
+    return gx_launch(NT, p, mx, mx, mx, tiles_n * max_jobs, s);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_nvfp4_gemm_bf16_workspace_bytes(int M, int K) { return gemm_mxf4_ws_bytes(M, K); }
+
+extern "C" int b200_nvfp4_gemm_bf16(float* y, const b200_wref* W, const void* x_bf16, int M, int N, int K,
+                                    void* ws, b200_stream stream) {
+    if (!y || !W || !x_bf16 || !ws || M < 1 || N < 1 || K < 1) return B200_EINVAL;
+    if (!W->packed) return B200_EINVAL;
+    if (K & 15) return B200_ESHAPE;
+    if ((uintptr_t)ws & 255) return B200_EALIGN;
+    return gemm_mxf4_dense(y, W, x_bf16, 0, M, N, K, ws, stream);
+}
+
+extern "C" int b200_nvfp4_quantize_tokens(const void* x, int x_is_f32, int M, int K, uint8_t* packed,
+                                          uint8_t* scale_step_major, float* gs, b200_stream stream) {
+    if (!x || !packed || !scale_step_major || !gs || M < 1 || K < 1) return B200_EINVAL;
+    if (K & 255) return B200_ESHAPE;
+    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 7) || ((uintptr_t)scale_step_major & 15) || ((uintptr_t)gs & 3)) return B200_EALIGN;
+    return quant_act_launch(x_is_f32 ? 1 : 0, x, nullptr, 0.f, nullptr, nullptr, M, M, K, packed, scale_step_major, (size_t)M, gs, stream);
+}

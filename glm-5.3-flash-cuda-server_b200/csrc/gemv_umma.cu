@@ -489,34 +489,15 @@ k_split_x(const float* __restrict__ x, int K, int stride, unsigned char* __restr
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
-        return (EncodeTiledFn)p;
-    }();
-    return fn;
-}
-// u8 matrix [rows, row_bytes]; box [box_bytes x box_rows].
+// u8 matrix [rows, row_bytes]; box [box_bytes x box_rows]; maps of weights are remembered (tmap.cu).
 static bool make_map(CUtensorMap* m, const void* base, int rows, size_t row_bytes, int box_bytes, int box_rows, bool swz) {
-    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
-    const cuuint32_t es[2] = {1, 1};
-    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tmap_u8_2d(m, base, (size_t)rows, row_bytes, box_bytes, box_rows, swz, true);
 }
 
 // Conditions: M = 1 (one activation row shared by all jobs), K % 256 == 0 and K <= 16384, 16-byte
 // aligned tensors and activation, at least 256 rows in total.
 static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre);
 static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaStream_t s);
-static bool scale_box(int K, int* box, int* swz);
 
 // Rows of the activations are taken in chunks that fit the shared memory (the B image takes M KB
 // per 256 k); every chunk size computes each row with the same arithmetic, so results do not
@@ -570,7 +551,7 @@ int nvfp4_multi_umma_ws(const GemvParams& g, int M, void* ws, cudaStream_t s) {
 // One launch: activation rows [m0, m0 + M) of every job.
 static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre) {
     const int K = g.K;
-    if ((K & 255) || K > 16384 || !encode_fn()) return B200_ENOTIMPL;
+    if ((K & 255) || K > 16384 || !tmap_available()) return B200_ENOTIMPL;
     if (M < 1 || M > UM_MAX_M) return B200_ENOTIMPL;
     for (int i = 0; i < g.n_jobs; ++i)
         if (((uintptr_t)g.j[i].x & 15) || ((uintptr_t)g.j[i].P & 15) || ((uintptr_t)g.j[i].S & 15)) return B200_ENOTIMPL;
@@ -622,13 +603,23 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     // rows were loaded (the extra accumulator rows are never stored).  Keep that read inside the
     // allocation for the last stage as well.
     if (p.stage_bytes + fixed < 16384) fixed = 16384 - p.stage_bytes;
-    cudaFuncAttributes fa;
-    int dev = 0, optin = 0;
     const bool gen = p.table != nullptr || p.max_m != 1 || p.T != 1;
     auto kern = gen ? k_gemv_umma<true> : k_gemv_umma<false>;
-    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemv_umma: attributes");
-    const size_t room = (size_t)optin - fa.sharedSizeBytes - 2048;    // 1 KB alignment slack + 1 KB system reserve
+    // static shared memory of the kernel and the device's opt-in limit: asked once per device and variant
+    static int attr_cache[64][2][2] = {};            // [device][variant] = {optin, static bytes + 1}
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return launch_failed("gemv_umma: cudaGetDevice");
+    int* ac = attr_cache[dev >= 0 && dev < 64 ? dev : 0][gen];
+    if (!ac[1]) {
+        cudaFuncAttributes fa;
+        int oi = 0;
+        if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
+            cudaDeviceGetAttribute(&oi, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return launch_failed("gemv_umma: attributes");
+        ac[0] = oi; ac[1] = (int)fa.sharedSizeBytes + 1;
+    }
+    const int optin = ac[0];
+    const size_t static_smem = (size_t)ac[1] - 1;
+    const size_t room = (size_t)optin - static_smem - 2048;    // 1 KB alignment slack + 1 KB system reserve
     if (fixed + 2 * (size_t)p.stage_bytes > room) return B200_ENOTIMPL;
     const int nsteps = p.T * nst;
     p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nsteps), (room - fixed) / p.stage_bytes);
@@ -649,7 +640,7 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     static bool ready_all[64][2] = {};               // the attribute is per device
     bool* ready = ready_all[dev >= 0 && dev < 64 ? dev : 0];
     if (!ready[gen]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - static_smem)) != cudaSuccess)
             return launch_failed("gemv_umma: cudaFuncSetAttribute");
         ready[gen] = true;
     }
@@ -661,12 +652,6 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     lc.attrs = at; lc.numAttrs = 1;
     if (cudaLaunchKernelEx(&lc, kern, p, maps) != cudaSuccess) return launch_failed("k_gemv_umma");
     return check_launch("k_gemv_umma");
-}
-
-static bool scale_box(int K, int* box, int* swz) {
-    if ((K / 16) % 128 == 0) { *box = 128; *swz = 1; return true; }
-    if (K / 16 <= 256) { *box = K / 16; *swz = 0; return true; }
-    return false;
 }
 
 // ---- activation rows split once for many CTAs ------------------------------------------------------
@@ -685,13 +670,13 @@ int umma_split_launch(const SplitJob* jobs, int n_jobs, int K, float limit, cuda
 }
 
 // ---- job-table launches (the MoE experts) ---------------------------------------------------------
-bool umma_shape_ok(int K) { int b, z; return !(K & 255) && K <= 16384 && scale_box(K, &b, &z) && encode_fn(); }
+bool umma_shape_ok(int K) { int b, z; return !(K & 255) && K <= 16384 && scale_box(K, &b, &z) && tmap_available(); }
 
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R) {
     int box = 0, swz = 0;
     if (!umma_shape_ok(K) || !scale_box(K, &box, &swz) || ((uintptr_t)P & 15) || ((uintptr_t)S & 15)) return B200_ENOTIMPL;
-    if (!make_map(static_cast<CUtensorMap*>(out_w), P, N, (size_t)K / 2, 128, R, true) ||
-        !make_map(static_cast<CUtensorMap*>(out_s), S, N, (size_t)K / 16, box, R, swz != 0)) return B200_ENOTIMPL;
+    if (!tmap_u8_2d(out_w, P, (size_t)N, (size_t)K / 2, 128, R, true, false) ||
+        !tmap_u8_2d(out_s, S, (size_t)N, (size_t)K / 16, box, R, swz != 0, false)) return B200_ENOTIMPL;
     return B200_OK;
 }
 

@@ -92,7 +92,12 @@ int b200_nvfp4_device_status(unsigned int* out, int clear);
  * kernel of the stream is still finishing; activations, scales and outputs are still only
  * touched after the previous kernel has completed.  Default 0 (also settable with the
  * environment variable B200_STABLE_WEIGHTS=1).  No counterpart in the reference. */
-enum { B200_OPT_STABLE_WEIGHTS = 1 };
+/* B200_OPT_PREFILL_FP4 (default 1; environment B200_PREFILL_FP4=0 turns it off): calls that carry
+ * scratch and 16 or more activation rows -- b200_nvfp4_gemm_ws with M >= 16, the MoE block with 16
+ * or more tokens on a prepared layer -- run the wide tensor-core GEMM, which quantises the
+ * activations to NVFP4 per token (see b200_nvfp4_gemm_bf16 for what that costs in accuracy).  With
+ * 0 those calls keep fp32-activation accuracy at every M, in passes of 8 rows over the weights. */
+enum { B200_OPT_STABLE_WEIGHTS = 1, B200_OPT_PREFILL_FP4 = 2 };
 int b200_nvfp4_set_option(int option, int value);
 
 /* y[M,N] = x[M,K] . W[N,K]^T.  Replaces glm5::gemm / glm5::gemv (reference include/gemv.h:29,
@@ -116,12 +121,38 @@ int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, int K, int dt
  * next call on the same stream may reuse it.  Results are bit-identical to the plain calls.
  * gemv_multi_ws wants all jobs to share one x; where the scratch cannot be used (M = 1, shapes the
  * tensor-core kernel does not take, ws == NULL) these run exactly as the plain calls.  No
- * counterpart in the reference, whose gemm has no workspace argument (include/gemv.h:75). */
+ * counterpart in the reference, whose gemm has no workspace argument (include/gemv.h:75).
+ * With M >= 16 and B200_OPT_PREFILL_FP4 on (the default), b200_nvfp4_gemm_ws runs the wide GEMM of
+ * b200_nvfp4_gemm_bf16 on the f32 rows instead (W read once per 256 rows, activations quantised to
+ * NVFP4 per token): the scratch size below covers it. */
 size_t b200_nvfp4_split_workspace_bytes(int M, int K);
 int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, int M, int N, int K,
                        int dtype, void* ws, b200_stream stream);
 int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
                              void* ws, b200_stream stream);
+
+/* The wide GEMM, for prefill and batched widths (M >= 16; any M >= 1 is accepted):
+ * y[M,N] (f32) = x[M,K] (bf16) . W[N,K]^T on tcgen05.mma kind::mxf4nvf4 with BOTH operands in NVFP4.
+ * W is read once for up to 256 rows of x (the reference's gemm streams W once per chunk of 4 rows,
+ * kernels/gemv.cu:369-396, include/gemv.h:65-75).  The activations are quantised to NVFP4 first, one
+ * token at a time (b200_nvfp4_quantize_tokens below), which costs about 9 % per-element activation
+ * error: results match deq(W) . deq(quant(x)) to 1e-3 and deviate from the exact product by a few
+ * per cent.  Callers that need fp32-activation accuracy use b200_nvfp4_gemm.  A token's result does
+ * not depend on the other rows of the batch.  Needs K % 256 == 0, K <= 16384, 16-byte aligned W and x;
+ * otherwise B200_ENOTIMPL.  ws: b200_nvfp4_gemm_bf16_workspace_bytes(M, K) bytes, 256-byte aligned,
+ * used only by this call's kernels.  No counterpart in the reference, which has no bf16-activation
+ * or tensor-core entry point. */
+size_t b200_nvfp4_gemm_bf16_workspace_bytes(int M, int K);
+int b200_nvfp4_gemm_bf16(float* y, const b200_wref* W, const void* x_bf16, int M, int N, int K,
+                         void* ws, b200_stream stream);
+
+/* Per-token activation quantiser of the wide GEMM: every row of x[M,K] (bf16 when x_is_f32 == 0, else
+ * f32) is quantised with the reference's quant_block rule (tools/requant_dense_nvfp4.py:53-68) and its
+ * own global scale gs[m] = 2688 / max(amax(row m), 1e-12) (:215 per row); bit-exact with that rule.
+ * packed [M, K/2]; scale is STEP-MAJOR, [K/256][M][16] (the 16 scale bytes of one row for 256
+ * consecutive k are contiguous); gs f32 [M].  K % 256 == 0. */
+int b200_nvfp4_quantize_tokens(const void* x, int x_is_f32, int M, int K, uint8_t* packed,
+                               uint8_t* scale_step_major, float* gs, b200_stream stream);
 
 /* Element-wise converters (reference include/gemv.h:61-62, kernels/gemv.cu:470-488). */
 int b200_f32_to_bf16(void* dst_bf16, const float* src, size_t n, b200_stream stream);

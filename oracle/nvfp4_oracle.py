@@ -126,6 +126,32 @@ def gemv(x, packed, scale, gs):
     return gemm(x, packed, scale, gs)[0]
 
 
+def quantize_rows(x_f32):
+    """Per-token activation quantisation of the block-scaled tensor-core GEMM: the reference's
+    quant_block rule (tools/requant_dense_nvfp4.py:53-68) applied to every row on its own, with the
+    row's own global scale 2688 / max(amax(row), 1e-12) (:215 evaluated per row).
+    Returns packed u8 [M, K/2], scale codes u8 [M, K/16], gs f32 [M]."""
+    x = np.atleast_2d(np.asarray(x_f32, np.float32))
+    M, K = x.shape
+    packed = np.zeros((M, K // 2), np.uint8); scale = np.zeros((M, K // GROUP), np.uint8); gs = np.zeros(M, np.float32)
+    for m in range(M):
+        gs[m] = global_scale(x[m])
+        packed[m:m + 1], scale[m:m + 1] = quantize(x[m:m + 1], gs[m])
+    return packed, scale, gs
+
+
+def dequant_rows(packed, scale, gs):
+    return np.concatenate([dequant(packed[m:m + 1], scale[m:m + 1], gs[m]) for m in range(packed.shape[0])], 0)
+
+
+def gemm_act_nvfp4(x, packed, scale, gs):
+    """y[M,N] = deq(quant_rows(x)) . deq(W)^T with fp64 accumulation: what a GEMM with BOTH operands in
+    NVFP4 computes (weights as stored, activations quantised per token).  The tensor-core prefill
+    path is judged against this; its distance from gemm() is the price of 4-bit activations."""
+    xq = dequant_rows(*quantize_rows(x)).astype(np.float64)
+    return xq @ dequant(packed, scale, gs).astype(np.float64).T
+
+
 def router_logits(x, router_w_bf16_bits):
     """x[M,H] fp32 times the bf16 router matrix [E,H] (reference kernels/moe.cu:643-647)."""
     Wr = bf16_bits_to_f32(router_w_bf16_bits).astype(np.float64)

@@ -139,6 +139,27 @@ def case_gemv():
     np.savez_compressed(os.path.join(OUT, 'gemv.npz'), **out)
 
 
+def case_gemm_act():
+    """Both operands in NVFP4: activations (bf16-valued) quantised one token at a time by the
+    reference's quant_block with the token's own global scale, then dequantise-and-matmul."""
+    out = {}
+    for i, (M, N, K) in enumerate([(5, 24, 256), (33, 40, 512)]):
+        rng = np.random.default_rng(2500 + i)
+        bits = to_bf16_bits(rng.normal(0.0, 0.02, (N, K)).astype(np.float32))
+        w, p, s, gs = ref_quant_tensor(bits)
+        xbits = to_bf16_bits((rng.normal(0.0, 1.0, (M, K)) * np.exp(rng.uniform(-3, 3, (M, 1)))).astype(np.float32))
+        xp, xs, xg, xd = [], [], [], []
+        for m in range(M):
+            _, pm, sm, gm_ = ref_quant_tensor(xbits[m:m + 1])
+            xp.append(pm); xs.append(sm); xg.append(gm_); xd.append(ref_dequant(pm, sm, gm_))
+        W = torch.from_numpy(ref_dequant(p, s, gs))
+        y = F.linear(torch.from_numpy(np.concatenate(xd, 0)), W).numpy()
+        out.update({'a%d_packed' % i: p, 'a%d_scale' % i: s, 'a%d_gs' % i: gs, 'a%d_xbits' % i: xbits,
+                    'a%d_xpacked' % i: np.concatenate(xp, 0), 'a%d_xscale' % i: np.concatenate(xs, 0),
+                    'a%d_xgs' % i: np.concatenate(xg, 0), 'a%d_y' % i: y})
+    np.savez_compressed(os.path.join(OUT, 'gemm_act.npz'), **out)
+
+
 def case_moe():
     """The MoE block of ref/gen_moe.py:62-96 at a small geometry, M tokens one at a time."""
     H, I, E, K, M = 256, 128, 16, 4, 3
@@ -189,7 +210,7 @@ def case_moe():
 
 
 if __name__ == '__main__':
-    case_tables(); case_quant(); case_edges(); case_gemv(); case_moe()
+    case_tables(); case_quant(); case_edges(); case_gemv(); case_gemm_act(); case_moe()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'):
             print('%-20s %8d bytes' % (f, os.path.getsize(os.path.join(OUT, f))))

@@ -78,3 +78,19 @@ def test_moe(golden):
     assert (np.abs(g) > float(z['limit'])).any()
     _, act = O.expert_mlp(z['x'][0:1], *experts[int(z['sel'][0][0])])
     assert O.rel_l2(act[0], z['act0'][0]) < 5e-6
+
+
+def test_gemm_act_golden(golden):
+    """Both operands in NVFP4: per-token activation codes bit for bit, product to fp32 rounding."""
+    z = golden('gemm_act')
+    for i in range(2):
+        x = O.bf16_bits_to_f32(z['a%d_xbits' % i])
+        p, s, gs = O.quantize_rows(x)
+        assert np.array_equal(p, z['a%d_xpacked' % i]) and np.array_equal(s, z['a%d_xscale' % i])
+        assert np.array_equal(gs.view(np.uint32), z['a%d_xgs' % i].view(np.uint32))
+        y = O.gemm_act_nvfp4(x, z['a%d_packed' % i], z['a%d_scale' % i], z['a%d_gs' % i])
+        ref = z['a%d_y' % i]
+        assert np.abs(y - ref).max() <= 2e-6 * max(1.0, np.abs(ref).max())
+        # the price of 4-bit activations against the exact product: a few per cent, never "close"
+        exact = O.gemm(x, z['a%d_packed' % i], z['a%d_scale' % i], z['a%d_gs' % i])
+        assert 0.01 < O.rel_l2(y, exact) < 0.2
