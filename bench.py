@@ -37,7 +37,6 @@ if UMMA:
     DTYPE = 'nvfp4 weights (e2m1 + e4m3 block scales) x activations as eight e2m1 digit columns (14 fractional bits of the row maximum), fp32 accumulate'
     MATH = 'tcgen05.mma kind::mxf4nvf4.block_scale.block16, accumulators in TMEM'
     KERNEL = 'k_gemv_umma<0>'
-    TRAFFIC = 29780480         # dram read + write bytes per launch, ncu capture of this command (summary under profiles/)
 else:
     DTYPE = 'nvfp4 weights (e2m1 + e4m3 scales), f16 products, f32 accumulate'
     MATH = 'fp32-mac' if os.environ.get('B200_NVFP4_MATH') == '1' else 'f16x2-chains'
@@ -50,6 +49,17 @@ import __graft_entry__ as G  # noqa: E402
 SIBLINGS = [4096, 4096, 4096, 512, 64, 32]
 K_HID = 4096
 L2_BYTES = 126e6
+
+
+def profiled_traffic():
+    """DRAM read + write bytes per launch of the headline kernel, from the committed ncu summary
+    (profiles/k_gemv_umma_siblings_M1.md, line 'roofline.traffic bytes per launch: N'); None if absent."""
+    import re
+    p = os.path.join(ROOT, 'profiles', 'k_gemv_umma_siblings_M1.md')
+    if not UMMA or not os.path.exists(p):
+        return None
+    m = re.search(r'roofline\.traffic bytes per launch:\s*(\d+)', open(p).read())
+    return int(m.group(1)) if m else None
 
 
 def measured_peaks():
@@ -120,9 +130,15 @@ def capture_steps(fns):
     return g
 
 
-def time_steps(fns, steps, warmup):
-    """Runs exactly `steps` timed steps, step i being fns[i % len(fns)]: graphs of about a hundred
-    steps (whole rotations), plus one shorter graph for the remainder.  Returns ms per step."""
+LAST_TIMING = {}
+LAST_TIMING_HEAD = {}
+
+
+def time_steps(fns, steps, warmup, replays=50):
+    """Times `steps` steps, step i being fns[i % len(fns)], captured back to back in CUDA graphs of at most
+    about a hundred launches (whole rotations plus one shorter graph for the remainder).  The K-step
+    region is replayed `replays` times, each replay bracketed by its own CUDA events on the launching
+    stream; returns the MEDIAN ms per step and leaves min / max / replays in LAST_TIMING."""
     for fn in fns:
         fn()                                        # outside capture: one-time attribute set-up
     torch.cuda.synchronize()
@@ -133,15 +149,21 @@ def time_steps(fns, steps, warmup):
     for _ in range(max(1, (warmup + G - 1) // G)):
         (full or rem).replay()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps // G if full is not None else 0):
-        full.replay()
-    if rem is not None:
-        rem.replay()
-    e1.record()
+    per = []
+    replays = max(1, min(replays, int(2.0e6 / max(steps, 1)) or 1))        # keep very long regions to a few replays
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(replays)]
+    for e0, e1 in evs:
+        e0.record()
+        for _ in range(steps // G if full is not None else 0):
+            full.replay()
+        if rem is not None:
+            rem.replay()
+        e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
+    per = sorted(e0.elapsed_time(e1) / steps for e0, e1 in evs)
+    LAST_TIMING.clear()
+    LAST_TIMING.update({'min_ms_per_step': per[0], 'max_ms_per_step': per[-1], 'replays': replays, 'steps_per_replay': steps})
+    return per[len(per) // 2]
 
 
 def make_weight(P, N, K, seed):
@@ -212,20 +234,58 @@ def bench_gemv_single(P, steps, warmup, copies):
     return ms, nv_bytes(N, K_HID) + K_HID * 4 + N * 4
 
 
-def bench_gemm_batch(P, M, steps, warmup, copies):
-    """[12288 x 4096] NVFP4 weights against M activation rows (a prefill-sized batch runs as passes of 8
-    rows over the weights).  Returns ms and the FLOPs of one call."""
-    N = 12288
-    base, _ = make_weight(P, N, K_HID, 998)
-    ws = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
-    x = torch.randn((M, K_HID), device='cuda')
+def bench_gemm_wide(P, N, M, steps, warmup):
+    """Prefill GEMM (configs[3]): NVFP4 [N x 4096] against M bf16 rows through b200_nvfp4_gemm_bf16 (per-token
+    activation quantiser + tcgen05 mxf4nvf4 GEMM, W read once).  Returns ms, flops, W-read-once bytes, and
+    the relative L2 distance of the result from the exact product (reported, not a pass/fail figure)."""
+    base, wb = make_weight(P, N, K_HID, 998)
+    copies = max(2, int(2.2 * L2_BYTES / nv_bytes(N, K_HID)) + 1)
+    ws_ = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
+    x = torch.randn((M, K_HID), device='cuda', generator=torch.Generator(device='cuda').manual_seed(3)).to(torch.bfloat16)
     y = torch.empty((M, N), device='cuda')
-    split = P.split_workspace(M, K_HID, x.device)
-    ms = time_steps([lambda W=W: P.gemm(W, x, y, ws=split) for W in ws], steps, warmup)
-    return ms, 2.0 * M * N * K_HID
+    scratch = P.gemm_bf16_workspace(M, K_HID, x.device)
+    ms = time_steps([lambda W=W: P.gemm_bf16(W, x, y, scratch) for W in ws_], steps, warmup)
+    exact = x.float() @ P.dequantize(base).t()
+    dev = ((y - exact).norm() / exact.norm()).item()
+    return ms, 2.0 * M * N * K_HID, nv_bytes(N, K_HID) + M * K_HID * 2 + M * N * 4, dev
 
 
-def build_moe_layers(P, n_layers, H, I, E, topk, seed):
+def bench_dense_mlp(P, steps, warmup):
+    """The dense-layer MLP of the reference (kernels/layer.cu:235-254) at its shapes, one token: gate and up
+    [12288 x 4096] as one 2-job launch, down [4096 x 12288] with the clamped SwiGLU applied as its
+    activations are staged (b200_dense_mlp)."""
+    H, I = K_HID, 12288
+    sets = []
+    for c in range(3):
+        g, _ = make_weight(P, I, H, 900 + 3 * c); u, _ = make_weight(P, I, H, 901 + 3 * c); d, _ = make_weight(P, H, I, 902 + 3 * c)
+        sets.append((g, u, d))
+    x = torch.randn((1, H), device='cuda'); y = torch.empty((1, H), device='cuda')
+    ws = P.dense_mlp_workspace(1, H, I, x.device)
+    ms = time_steps([lambda t=t: P.dense_mlp(x, t[0], t[1], t[2], 10.0, y, ws) for t in sets], steps, warmup)
+    return ms, 2 * nv_bytes(I, H) + nv_bytes(H, I) + 2 * H * 4
+
+
+def bench_kda_groups(P, steps, warmup):
+    """The fused sibling groups of the linear-attention layer with their real shapes (reference
+    kernels/kda.cu:235-266, tests/gate_gemv_multi.cu:54-61)."""
+    out = {}
+    groups = {'kda_qkv_8192x4096_x3': ([8192, 8192, 8192], 4096, False), 'kda_lowrank_128_128_64_x4096': ([128, 128, 64], 4096, False),
+              'kda_up_8192x128_x2_own_x': ([8192, 8192], 128, True)}
+    for name, (Ns, K, own_x) in groups.items():
+        nb = sum(nv_bytes(n, K) for n in Ns)
+        copies = max(2, min(64, int(2.2 * L2_BYTES / nb) + 1))
+        sets = [[make_weight(P, n, K, 800 + i)[0] for i, n in enumerate(Ns)]]
+        sets += [[clone_weight(P, W) for W in sets[0]] for _ in range(copies - 1)]
+        xs = [torch.randn((1, K), device='cuda') for _ in Ns] if own_x else [torch.randn((1, K), device='cuda')] * len(Ns)
+        ys = [torch.empty((1, n), device='cuda') for n in Ns]
+        jobs = [P.make_jobs(ws, xs, ys) for ws in sets]
+        ms = time_steps([lambda ws=ws, j=j: P.gemv_multi(ws, xs, 1, ys, jobs=j) for ws, j in zip(sets, jobs)], steps, warmup)
+        b = nb + (len(Ns) if own_x else 1) * K * 4 + sum(Ns) * 4
+        out[name] = {'us': ms * 1e3, 'bytes': b, 'tbps': b / (ms * 1e-3) / 1e12, 'weight_copies_in_rotation': copies}
+    return out
+
+
+def build_moe_layers(P, n_layers, H, I, E, topk, seed, zipf=False):
     layers = []
     for l in range(n_layers):
         gen = torch.Generator(device='cuda').manual_seed(seed + l)
@@ -238,6 +298,8 @@ def build_moe_layers(P, n_layers, H, I, E, topk, seed):
             ex.append(tuple(tr))
         router = (torch.randn((E, H), generator=gen, device='cuda') * 0.02).to(torch.bfloat16)
         bias = torch.randn(E, generator=gen, device='cuda') * 0.1
+        if zipf:
+            bias = bias + zipf_bias(E).cuda()
         layers.append(P.MoeLayer(router, bias, ex[:E], ex[E], topk, H, I))
     return layers
 
@@ -285,84 +347,144 @@ def zipf_bias(E, s=1.1, seed=4, strength=0.08):
     return torch.from_numpy((strength * np.log(p / p.mean())).astype(np.float32))
 
 
-def bench_ep(P, a, rank, local, world, peak):
-    """Expert-parallel MoE (configs[4]): T tokens x hidden 4096, 144 experts sharded over the ranks,
-    top-8 + replicated shared expert, 3 stacked layers, x <- rmsnorm(x + y) between layers."""
+def bench_ep(P, a, rank, local, world, peak, T):
+    """Expert-parallel MoE (configs[4]) through the library's C++/NCCL context (b200_ep_*): T tokens x hidden
+    4096, 144 experts sharded over the ranks, top-8 + replicated shared expert, Zipf(1.1) routing bias, 3
+    stacked layers, x <- rmsnorm(x + y) between layers.  world == 1 runs the same code without NCCL.
+    Returns the result dict on rank 0 (None elsewhere); raises SystemExit on a parity failure."""
     import torch.distributed as dist
     dev = torch.device('cuda', local)
-    T, Lyr, E, topk, H, I = a.ep_tokens, 3, 144, 8, 4096, 1536
+    Lyr, E, topk, H, I = 3, 144, 8, 4096, 1536
     Tl = T // world
     pb = zipf_bias(E)
-    layers = [P.ep_gpu.RankLayer(50, l, E, topk, H, I, rank, world, dev, popularity_bias=pb) for l in range(Lyr)]
+    layers = [P.ep_gpu.RankLayer(50, l, E, topk, H, I, rank, world, dev, max_tokens=Tl, popularity_bias=pb) for l in range(Lyr)]
     g = torch.Generator(device=dev).manual_seed(123)
     x_all = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16).float()      # bf16-valued activations
     x0 = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
+    ys = [torch.empty((Tl, H), device=dev) for _ in range(Lyr)]
+    sel = torch.empty((Tl, topk), dtype=torch.int32, device=dev); wts = torch.empty((Tl, topk), device=dev)
+    barrier = dist.barrier if world > 1 else (lambda: None)
 
     def step(x):
-        nb = 0
-        for L in layers:
-            y, _, _ = L.forward(x)
-            nb += L.step_bytes(Tl)
+        for L, y in zip(layers, ys):
+            L.forward(x, y, sel, wts)
             x = x + y
             x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)
-        return x, nb
+        return x
     for _ in range(a.warmup):
         step(x0)
-    torch.cuda.synchronize(); dist.barrier()
+    torch.cuda.synchronize(); barrier()
+    steps = max(3, min(a.steps, 50))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as cs:
         e0.record()
-        nb = 0
-        for _ in range(a.steps):
-            _, nb = step(x0)
+        for _ in range(steps):
+            step(x0)
         e1.record()
         torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    b = torch.tensor([float(nb)], device=dev, dtype=torch.float64)
-    dist.all_reduce(b)
-    ms = t.item() / a.steps
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    # statistics of the last step (outside the timed region): bytes, load, phase times
+    stats = [L.ctx.stats() for L in layers]
+    nb = float(sum(L.step_bytes(Tl, st) for L, st in zip(layers, stats)))
+    vec = torch.tensor([ms, nb, float(sum(st['recv_rows'] for st in stats)), float(sum(st['dispatch_bytes_out'] for st in stats)),
+                        float(sum(st['combine_bytes_in'] for st in stats)), float(sum(st['dispatch_us'] for st in stats)),
+                        float(sum(st['combine_us'] for st in stats)), float(sum(st['experts_us'] for st in stats))], device=dev, dtype=torch.float64)
+    allv = [torch.zeros_like(vec) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(allv, vec)
+    else:
+        allv = [vec]
+    allv = torch.stack(allv).cpu().numpy()
+    ms = float(allv[:, 0].max())                       # the slowest rank sets the time
     # end to end: tokens from pinned host memory in, outputs back, every step
     xh = x0.cpu().pin_memory(); yh = torch.empty_like(xh).pin_memory(); xd = torch.empty_like(x0)
-    n_e2e = max(1, min(a.steps, 10))
-    torch.cuda.synchronize(); dist.barrier()
+    n_e2e = max(1, min(steps, 10))
+    torch.cuda.synchronize(); barrier()
     t0 = time.perf_counter()
     for _ in range(n_e2e):
         xd.copy_(xh, non_blocking=True)
-        out, _ = step(xd)
+        out = step(xd)
         yh.copy_(out, non_blocking=True)
         torch.cuda.synchronize()
-    dist.barrier()
+    barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
-    # parity of the sharded layer against the single-GPU entry point on rank 0's tokens
-    y_ep, sel_ep, _ = layers[0].forward(x0)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_ms = t.item()
+    # parity of the sharded layer on rank 0's tokens: against the single-GPU entry point on the full layer, and
+    # against the CPU oracle on the first tokens (both with the activations quantised as the wide GEMM does)
+    y_ep, sel_ep, wts_ep = layers[0].forward(x0)
     par = None
     if rank == 0:
         full = [P.ep_gpu.expert_weights(50, 0, e, H, I, dev) for e in range(E + 1)]
         ref_layer = P.MoeLayer(layers[0].router, layers[0].bias, full[:E], full[E], topk, H, I)
-        if layers[0].tensor_core: P.moe_prepare(ref_layer)
-        y_ref, sel_ref, _ = P.moe_forward(ref_layer, x0)
-        par = {'rel_l2': ((y_ep - y_ref).norm() / y_ref.norm()).item(), 'sel_equal': bool(torch.equal(sel_ep, sel_ref))}
-    stats = [L.ep.last_stats for L in layers]
+        P.moe_prepare(ref_layer)
+        y_ref, sel_ref, _ = P.moe_forward(ref_layer, x0[:max(16, min(Tl, 64))].contiguous())
+        n = y_ref.shape[0]
+        par = {'rel_l2_vs_single_gpu': ((y_ep[:n] - y_ref).norm() / y_ref.norm()).item(), 'sel_equal': bool(torch.equal(sel_ep[:n], sel_ref))}
+        if T == a.ep_tokens[0]:
+            O = G.load_oracle()
+            rows = [0, 1]
+            sel_h, wts_h = sel_ep[rows].cpu().numpy(), wts_ep[rows].cpu().numpy()
+            need = set(sel_h.ravel().tolist())
+            host = [tuple(w.numpy() for w in full[e]) if (e in need or e == E) else None for e in range(E + 1)]
+            yo = O.moe_experts_act_nvfp4(x0[rows].cpu().numpy(), sel_h, wts_h, host[:E], host[E])
+            par['rel_l2_vs_oracle_first_tokens'] = O.rel_l2(y_ep[rows].cpu().numpy(), yo)
+        P.moe_release(ref_layer)
+        del full, ref_layer
+    status = P.device_status()
+    for L in layers:
+        L.close()
+    del layers
+    torch.cuda.empty_cache()
     if rank != 0:
-        return
-    total_b = b.item()
-    val = total_b / (ms * 1e-3) / 1e12
-    return ({
-        'metric': 'nvfp4_moe_ep_hbm_tbps', 'value': val, 'unit': 'TB/s', 'n_gpus': world, 'steps': a.steps, 'warmup': a.warmup,
-        'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
-        'dtype': DTYPE, 'data': 'synthetic',
+        return None
+    bad = par['rel_l2_vs_single_gpu'] > 1e-3 or not par['sel_equal'] or par.get('rel_l2_vs_oracle_first_tokens', 0.0) > 1e-3
+    total_b = float(allv[:, 1].sum())
+    rows = allv[:, 2]
+    res = {
+        'metric': 'nvfp4_moe_ep_tokens_per_s', 'value': T / (ms * 1e-3), 'unit': 'tokens/s', 'n_gpus': world, 'tokens': T, 'steps': steps,
+        'ms_per_step': ms, 'us_per_layer': ms * 1e3 / Lyr, 'scaling': 'strong',
         'config': {'workload': 'expert-parallel MoE: %d tokens x 4096, 144 experts (%d per GPU), top-8 + shared expert, Zipf(1.1) routing bias, 3 stacked layers (configs[4])' % (T, E // world),
-                   'l2': 'inputs larger than L2: %.1f GB of expert weights per rank' % (Lyr * (E // world + 1) * layers[0].expert_bytes / 1e9),
-                   'collective': 'NCCL all_to_all_single: counts, token rows (fp32), expert ids; reverse for outputs'},
-        'tokens_per_s': T / (ms * 1e-3), 'us_per_layer': ms * 1e3 / Lyr,
-        'roofline': {'bound': 'hbm', 'kernel': 'k_gemv_umma<1> (experts, rows grouped by expert)' if layers[0].tensor_core else 'k_expert_act', 'achieved': val * 1e3 / world, 'peak': peak, 'unit': 'GB/s per GPU',
-                     'frac': val * 1e3 / world / peak, 'traffic': None},
-        'e2e': {'value': total_b / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
-                'h2d_bytes_per_step': Tl * H * 4 * world, 'd2h_bytes_per_step': Tl * H * 4 * world},
-        'gpu_launches': a.steps * Lyr * (16 if layers[0].tensor_core else 6), 'device_status': P.device_status(), 'clocks': cs.summary(), 'ep_parity_vs_single_gpu': par, 'rank0_layer_stats': stats,
-    })
+                   'collective': 'one ncclAllGather of counts + ONE grouped ncclSend/ncclRecv round each way per layer (bf16 rows + ids out, f32 rows back); host code in C++ inside the library' if world > 1 else 'none (one rank)',
+                   'math': 'experts on the wide tensor-core GEMM (both operands NVFP4), rows grouped by local expert'},
+        'hbm_bytes_per_step_all_gpus': total_b, 'hbm_tbps_all_gpus': total_b / (ms * 1e-3) / 1e12,
+        'roofline': {'bound': 'hbm', 'kernel': 'k_gemm_mxf4 (local experts)', 'achieved': total_b / world / (ms * 1e-3) / 1e9, 'peak': peak,
+                     'unit': 'GB/s per GPU', 'frac': total_b / world / (ms * 1e-3) / 1e9 / peak},
+        'load_rows_per_gpu_max_over_mean': float(rows.max() / max(rows.mean(), 1e-9)),
+        'nvlink': {'dispatch_bytes_out_per_gpu_per_layer': float(allv[:, 3].mean() / Lyr), 'combine_bytes_in_per_gpu_per_layer': float(allv[:, 4].mean() / Lyr),
+                   'dispatch_us_per_layer_max': float(allv[:, 5].max() / Lyr), 'combine_us_per_layer_max': float(allv[:, 6].max() / Lyr),
+                   'dispatch_gbps_per_gpu': float(allv[:, 3].mean() / max(allv[:, 5].max(), 1e-9) / 1e3),
+                   'combine_gbps_per_gpu': float(allv[:, 4].mean() / max(allv[:, 6].max(), 1e-9) / 1e3), 'peak_gbps_per_direction': 900.0},
+        'experts_us_per_layer_max': float(allv[:, 7].max() / Lyr),
+        'e2e': {'value': T / (e2e_ms * 1e-3), 'unit': 'tokens/s', 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': T * H * 4, 'd2h_bytes_per_step': T * H * 4},
+        'parity': par, 'parity_ok': not bad, 'device_status': status, 'clocks': cs.summary(),
+    }
+    return res
+
+
+def run_ep_all(P, a, rank, local, world, peak):
+    """The expert-parallel layer at every requested token count; remembers the one-GPU result of this box so
+    that later runs at N > 1 can state their speed-up over it."""
+    out = {}
+    n1_path = os.path.join('/tmp', 'b200_nvfp4_ep_n1.json')
+    n1 = json.load(open(n1_path)) if world > 1 and os.path.exists(n1_path) else {}
+    for T in a.ep_tokens:
+        if T % world:
+            continue
+        r = bench_ep(P, a, rank, local, world, peak, T)
+        if r is None:
+            continue
+        if str(T) in n1:
+            r['speedup_vs_n1'] = n1[str(T)] / r['ms_per_step']
+            r['efficiency_vs_n1'] = r['speedup_vs_n1'] / world
+        out['T%d' % T] = r
+    if rank == 0 and world == 1:
+        try:
+            json.dump({str(r['tokens']): r['ms_per_step'] for r in out.values()}, open(n1_path, 'w'))
+        except OSError:
+            pass
+    return out
 
 
 # ---- CPU baseline: the reference's CPU path restated (torch dequantise, then matmul) ------------
@@ -438,10 +560,11 @@ def main():
     ap.add_argument('--warmup', type=int, default=50)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--quick', action='store_true', help='headline only, no sub-workloads')
-    ap.add_argument('--ep-tokens', type=int, default=256, help='tokens per step of the expert-parallel workload (N > 1)')
-    ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,siblings,moe,quant)')
+    ap.add_argument('--ep-tokens', default='256,2048', help='token counts of the expert-parallel workload')
+    ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,lm_head,siblings,gemm,dense_mlp,kda,moe,moe_prefill,ep,quant)')
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    a.ep_tokens = [int(t) for t in str(a.ep_tokens).split(',') if t]
     rank = int(os.environ.get('RANK', '0'))
     local = int(os.environ.get('LOCAL_RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -466,6 +589,7 @@ def main():
         copies = 10
         torch.cuda.synchronize(); dist.barrier()
         ms, nbytes, clocks, state = bench_siblings(P, 1, a.steps, a.warmup, copies, sampler_index=local)
+        LAST_TIMING_HEAD.update(LAST_TIMING)
         torch.cuda.synchronize(); dist.barrier()
         e2e_ms, h2d, d2h = bench_siblings_e2e(P, state, min(a.steps, 2000), a.warmup)
         t = torch.tensor([ms, e2e_ms], device='cuda', dtype=torch.float64)
@@ -474,7 +598,7 @@ def main():
         del state
         torch.cuda.empty_cache()
         dist.barrier()
-        ep = bench_ep(P, a, rank, local, world, peak)
+        ep = run_ep_all(P, a, rank, local, world, peak)
         dist.barrier()
         if rank == 0:
             value = world * nbytes / (ms * 1e-3) / 1e12
@@ -488,18 +612,22 @@ def main():
                            'launch': 'steps captured back to back in CUDA graphs; programmatic dependent launch; weights declared stable',
                            'math': MATH},
                 'roofline': {'bound': 'hbm', 'kernel': KERNEL, 'achieved': value * 1e3 / world, 'peak': peak, 'unit': 'GB/s per GPU',
-                             'frac': value * 1e3 / world / peak, 'peak_kind': peak_kind, 'traffic': TRAFFIC if UMMA else None,
+                             'frac': value * 1e3 / world / peak, 'peak_kind': peak_kind, 'traffic': profiled_traffic(),
                              'algorithmic_bytes_per_launch': nbytes},
                 'e2e': {'value': world * nbytes / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
                         'h2d_bytes_per_step': h2d * world, 'd2h_bytes_per_step': d2h * world},
                 'cpu_baseline': None, 'gpu_launches': a.steps, 'device_status': P.device_status(), 'clocks': clocks,
+                'timing': dict(LAST_TIMING_HEAD),
                 'ep_moe': ep,
             }))
         dist.destroy_process_group()
+        if rank == 0 and any(not r['parity_ok'] for r in ep.values()):
+            raise SystemExit('expert-parallel parity failed: %s' % {k: r['parity'] for k, r in ep.items()})
         return
 
     copies = 10                                        # 10 x 29.7 MB = 297 MB per rotation, > 2x L2
     ms, nbytes, clocks, state = bench_siblings(P, 1, a.steps, a.warmup, copies, sampler_index=local)
+    LAST_TIMING_HEAD.update(LAST_TIMING)
     value = nbytes / (ms * 1e-3) / 1e12
     e2e_ms, h2d, d2h = bench_siblings_e2e(P, state, min(a.steps, 2000), a.warmup)
     sub = {}
@@ -525,9 +653,22 @@ def main():
             sub['siblings_M%d' % M] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
                                        'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
     if want('gemm'):
-        for M in (32, 128):
-            m, fl = bench_gemm_batch(P, M, max(20, sub_steps // 10), a.warmup, copies)
-            sub['gemm_12288x4096_M%d' % M] = {'us': m * 1e3, 'tflops': fl / (m * 1e-3) / 1e12, 'passes_of_8_rows': M // 8}
+        fp4_peak = 4 * 1652.6                        # dense FP4 tensor peak taken as 4x the measured bf16 burst (TFLOP/s)
+        for N in (12288, 4096):
+            for M in (32, 128, 512):
+                m, fl, b, dev_exact = bench_gemm_wide(P, N, M, max(20, sub_steps // 5), a.warmup)
+                sub['gemm_bf16_%dx4096_M%d' % (N, M)] = {
+                    'us': m * 1e3, 'min_us': LAST_TIMING['min_ms_per_step'] * 1e3, 'tflops': fl / (m * 1e-3) / 1e12,
+                    'frac_of_fp4_peak_4x_bf16': fl / (m * 1e-3) / 1e12 / fp4_peak, 'bytes_w_read_once': b,
+                    'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak, 'rel_l2_vs_exact_product': dev_exact,
+                    'launches_per_step': 2, 'kernels': 'k_quant_act + k_gemm_mxf4'}
+    if want('dense_mlp'):
+        m, b = bench_dense_mlp(P, max(50, sub_steps // 5), a.warmup)
+        sub['dense_mlp_12288_M1'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12, 'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
+    if want('kda'):
+        for k, v in bench_kda_groups(P, sub_steps, a.warmup).items():
+            v['frac_of_measured_hbm'] = v['tbps'] * 1e3 / peak
+            sub[k] = v
     if want('moe'):
         layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4000)
         for M, prep in ((1, True), (4, True), (8, True), (64, True), (1, False)):
@@ -537,6 +678,19 @@ def main():
                 'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak,
                 'experts': 'tensor-core (prepared layer)' if prep else 'CUDA-core'}
         del layers
+    if want('moe_prefill'):
+        # grouped-expert GEMM under Zipf(1.1) routing on one GPU (configs[3]): prefill widths on a prepared layer
+        layers = build_moe_layers(P, 3, 4096, 1536, 144, 8, 4100, zipf=True)
+        for M in (32, 128, 512):
+            m, b, d = bench_moe(P, layers, M, max(20, sub_steps // 10), a.warmup, True)
+            fl = 2.0 * M * 9 * 3 * 1536 * 4096
+            sub['moe_prefill_zipf_I1536_M%d' % M] = {
+                'us_per_layer': m * 1e3, 'bytes': b, 'distinct_routed': d, 'tbps': b / (m * 1e-3) / 1e12,
+                'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak, 'tflops': fl / (m * 1e-3) / 1e12,
+                'experts': 'wide tensor-core GEMM, rows grouped by expert'}
+        del layers
+        torch.cuda.empty_cache()
+    ep = run_ep_all(P, a, rank, local, 1, peak) if want('ep') else {}
     if want('quant'):
         m, b = bench_quantize(P, min(sub_steps, 200), a.warmup)
         sub['quantize_12288x4096'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12,
@@ -552,16 +706,19 @@ def main():
                    'launch': 'steps captured back to back in CUDA graphs; programmatic dependent launch; weights declared stable',
                    'math': MATH},
         'roofline': {'bound': 'hbm', 'kernel': KERNEL, 'achieved': value * 1e3, 'peak': peak, 'unit': 'GB/s',
-                     'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': TRAFFIC if UMMA else None,
+                     'frac': value * 1e3 / peak, 'peak_kind': peak_kind, 'traffic': profiled_traffic(),
                      'algorithmic_bytes_per_launch': nbytes},
         'e2e': {'value': nbytes / (e2e_ms * 1e-3) / 1e12, 'unit': 'TB/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
         'cpu_baseline': {'value': nbytes / cpu_s / 1e12, 'unit': 'TB/s', 'cores': torch.get_num_threads(),
                          'kind': 'port', 'sample': '%d steps of the same six-sibling workload, torch dequantise + linear' % cpu_n,
                          'ms_per_step': cpu_s * 1e3},
-        'gpu_launches': a.steps, 'device_status': P.device_status(), 'clocks': clocks, 'sub': sub,
+        'gpu_launches': a.steps, 'device_status': P.device_status(), 'clocks': clocks, 'timing': dict(LAST_TIMING_HEAD),
+        'sub': sub, 'ep_moe': ep,
     }
     print(json.dumps(out))
+    if any(not r['parity_ok'] for r in ep.values()):
+        raise SystemExit('expert-parallel parity failed: %s' % {k: r['parity'] for k, r in ep.items()})
 
 
 def reference_arm(a, P, rank, peak):

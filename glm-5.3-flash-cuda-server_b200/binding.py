@@ -36,6 +36,13 @@ class MoeLayerC(C.Structure):
                 ('norm_topk', C.c_int)]
 
 
+class EpStats(C.Structure):
+    _fields_ = [('tokens', C.c_int), ('recv_rows', C.c_int), ('sent_remote_rows', C.c_int), ('recv_remote_rows', C.c_int),
+                ('local_experts_touched', C.c_int), ('pad', C.c_int), ('dispatch_bytes_out', C.c_ulonglong),
+                ('combine_bytes_in', C.c_ulonglong), ('plan_us', C.c_float), ('dispatch_us', C.c_float),
+                ('experts_us', C.c_float), ('combine_us', C.c_float), ('total_us', C.c_float), ('pad2', C.c_float)]
+
+
 class B200Error(RuntimeError):
     pass
 
@@ -51,6 +58,7 @@ def lib():
         L.b200_nvfp4_strerror.restype = C.c_char_p; L.b200_nvfp4_strerror.argtypes = [ci]
         L.b200_nvfp4_version.restype = ci
         L.b200_nvfp4_device_status.argtypes = [C.POINTER(C.c_uint), ci]
+        L.b200_nvfp4_selftest_bounded_wait.argtypes = [vp]
         L.b200_nvfp4_gemm.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp]
         L.b200_nvfp4_gemv_multi.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp]
         L.b200_nvfp4_split_workspace_bytes.restype = st; L.b200_nvfp4_split_workspace_bytes.argtypes = [ci, ci]
@@ -59,6 +67,8 @@ def lib():
         L.b200_nvfp4_gemm_bf16_workspace_bytes.restype = st; L.b200_nvfp4_gemm_bf16_workspace_bytes.argtypes = [ci, ci]
         L.b200_nvfp4_gemm_bf16.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, vp, vp]
         L.b200_nvfp4_quantize_tokens.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
+        L.b200_dense_mlp_workspace_bytes.restype = st; L.b200_dense_mlp_workspace_bytes.argtypes = [ci, ci, ci]
+        L.b200_dense_mlp.argtypes = [vp, C.POINTER(WRef), C.POINTER(WRef), C.POINTER(WRef), ci, ci, C.c_float, vp, vp, ci, vp]
         L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
         L.b200_bf16_to_f32.argtypes = [vp, vp, st, vp]
         L.b200_nvfp4_quantize.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
@@ -69,6 +79,11 @@ def lib():
         L.b200_moe_experts.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, vp, ci, vp]
         L.b200_moe_forward_static.argtypes = [vp, C.POINTER(MoeLayerC), vp, vp, vp, ci, vp]
         L.b200_moe_static_ws_limit.restype = st
+        L.b200_ep_unique_id.argtypes = [vp]
+        L.b200_ep_create.argtypes = [C.POINTER(vp), vp, ci, ci, C.POINTER(MoeLayerC), C.POINTER(MoeLayerC), C.POINTER(MoeLayerC), ci]
+        L.b200_ep_forward.argtypes = [vp, vp, vp, vp, vp, ci, vp]
+        L.b200_ep_last_stats.argtypes = [vp, C.POINTER(EpStats)]
+        L.b200_ep_destroy.argtypes = [vp]
         L.b200_moe_prepare.argtypes = [C.POINTER(MoeLayerC)]
         L.b200_moe_release.argtypes = [C.POINTER(MoeLayerC)]
         _lib = L
@@ -76,10 +91,11 @@ def lib():
 
 
 ENOTIMPL = 6
-EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
-           'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
+EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_selftest_bounded_wait', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
+           'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_dense_mlp_workspace_bytes', 'b200_dense_mlp', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
-           'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release']
+           'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release',
+           'b200_ep_unique_id', 'b200_ep_create', 'b200_ep_forward', 'b200_ep_last_stats', 'b200_ep_destroy']
 
 
 def check(rc, what):
@@ -185,6 +201,24 @@ def quantize_tokens(x, stream=None):
     check(lib().b200_nvfp4_quantize_tokens(_ptr(x), 1 if x.dtype == torch.float32 else 0, M, K, _ptr(packed), _ptr(sfb), _ptr(gs),
                                            stream_ptr(stream)), 'b200_nvfp4_quantize_tokens')
     return packed, sfb.permute(1, 0, 2).reshape(M, K // 16).contiguous(), gs
+
+
+def dense_mlp_workspace(M, hidden, inter, device):
+    return torch.empty(lib().b200_dense_mlp_workspace_bytes(M, hidden, inter), dtype=torch.uint8, device=device)
+
+
+def dense_mlp(x, gate, up, down, limit=10.0, y=None, ws=None, stream=None):
+    """y = down . (silu(min(gate.x, limit)) * clamp(up.x, -limit, limit)); x [M, hidden] f32."""
+    M, H = x.shape
+    I = gate.N
+    if y is None:
+        y = torch.empty((M, H), dtype=torch.float32, device=x.device)
+    if ws is None:
+        ws = dense_mlp_workspace(M, H, I, x.device)
+    g, u, d = gate.wref(), up.wref(), down.wref()
+    check(lib().b200_dense_mlp(_ptr(x), C.byref(g), C.byref(u), C.byref(d), H, I, float(limit), _ptr(y), _ptr(ws), M, stream_ptr(stream)),
+          'b200_dense_mlp')
+    return y
 
 
 def gemv(W, x, y=None, stream=None):
@@ -333,3 +367,39 @@ def moe_forward_static(layer, x, y=None, sel=None, wts=None, stream=None):
     check(lib().b200_moe_forward_static(_ptr(x2), C.byref(layer.c), _ptr(y), _ptr(sel), _ptr(wts), M, stream_ptr(stream)),
           'b200_moe_forward_static')
     return y, sel, wts
+
+
+def ep_unique_id():
+    """128 bytes that identify a new NCCL communicator (call on one rank, hand to all)."""
+    buf = C.create_string_buffer(128)
+    check(lib().b200_ep_unique_id(buf), 'b200_ep_unique_id')
+    return buf.raw
+
+
+class EpContext:
+    """An expert-parallel layer context of the library (b200_ep_*): this object only holds the handle."""
+
+    def __init__(self, router, local, shared, rank, world, max_tokens, unique_id=None):
+        self.h = C.c_void_p(0)
+        self.router, self.local, self.shared = router, local, shared      # keep the tables alive
+        idbuf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        check(lib().b200_ep_create(C.byref(self.h), idbuf, rank, world, C.byref(router.c), C.byref(local.c),
+                                   C.byref(shared.c) if shared is not None else None, max_tokens), 'b200_ep_create')
+
+    def forward(self, x, y=None, sel=None, wts=None, stream=None):
+        T, dev = x.shape[0], x.device
+        y = torch.empty((T, self.router.hidden), dtype=torch.float32, device=dev) if y is None else y
+        sel = torch.empty((T, self.router.topk), dtype=torch.int32, device=dev) if sel is None else sel
+        wts = torch.empty((T, self.router.topk), dtype=torch.float32, device=dev) if wts is None else wts
+        check(lib().b200_ep_forward(self.h, _ptr(x), _ptr(y), _ptr(sel), _ptr(wts), T, stream_ptr(stream)), 'b200_ep_forward')
+        return y, sel, wts
+
+    def stats(self):
+        st = EpStats()
+        check(lib().b200_ep_last_stats(self.h, C.byref(st)), 'b200_ep_last_stats')
+        return {k: getattr(st, k) for k, _ in EpStats._fields_ if not k.startswith('pad')}
+
+    def close(self):
+        if self.h:
+            check(lib().b200_ep_destroy(self.h), 'b200_ep_destroy')
+            self.h = C.c_void_p(0)

@@ -67,7 +67,11 @@ size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M);
 struct MoePlan;
 int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, int M, MoePlan* q, int* R_gu, int* R_d);
 int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
-                     void* scratch, int M, cudaStream_t s, bool planned);
+                     void* scratch, int M, cudaStream_t s, bool planned, int wide);
+// moe.cu: b200_moe_experts with the choice between the exact experts and the wide GEMM made by the caller
+// (wide = 1 / 0), or by the row count (-1): an expert-parallel rank decides by the tokens of ALL ranks.
+int moe_experts_mode(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                     void* ws, int M, cudaStream_t s, int wide);
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
 int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s);
 
@@ -81,7 +85,7 @@ bool gemm_mxf4_shape_ok(int K);
 int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s);
 int quant_act_launch(int mode, const void* x, const void* x2, float limit, const int* src_row, const int* m_dev, int M,
                      int rows_launch, int K, unsigned char* xq, unsigned char* sfb, size_t sfb_rows, float* gsx, cudaStream_t s);
-int gemm_mxf4_table(const GxJob* table, int max_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
+int gemm_mxf4_table(const GxJob* table, int max_jobs, long expected_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
                     const unsigned char* sfb, size_t sfb_rows, cudaStream_t s);
 
 }  // namespace b200

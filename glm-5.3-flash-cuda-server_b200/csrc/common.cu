@@ -1,5 +1,6 @@
 // common.cu -- error reporting and cached device attributes.
 #include "b200_internal.h"
+#include "tma_pipe.cuh"
 #include <cstdio>
 #include <cstdlib>
 
@@ -78,6 +79,8 @@ extern "C" const char* b200_nvfp4_strerror(int code) {
         case B200_ELAUNCH: return "CUDA launch failed";
         case B200_ELIMIT: return "size beyond the documented maximum";
         case B200_ENOTIMPL: return "not implemented";
+        case B200_ETIMEOUT: return "a bounded wait ran out";
+        case B200_ECOMM: return "NCCL missing or failed";
         default: return "unknown error";
     }
 }
@@ -88,6 +91,22 @@ extern "C" int b200_nvfp4_set_option(int option, int value) {
     if (option == B200_OPT_STABLE_WEIGHTS) { b200::set_stable_weights(value); return B200_OK; }
     if (option == B200_OPT_PREFILL_FP4) { b200::g_prefill_fp4 = value ? 1 : 0; return B200_OK; }
     return B200_EINVAL;
+}
+
+// One thread waits, with the library's bounded wait, on a barrier that nobody ever arrives at: the wait gives
+// up after its limit (about a second), records site 15 in the status word, and the kernel returns.
+__global__ void k_selftest_wait(unsigned int* status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { b200::mbar_init(b200::smem_u32(&bar), 1); b200::mbar_fence_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) b200::mbar_wait(b200::smem_u32(&bar), 0, status, 15);
+}
+
+extern "C" int b200_nvfp4_selftest_bounded_wait(b200_stream stream) {
+    unsigned int* p = b200::device_status_ptr();
+    if (!p) return B200_ELAUNCH;
+    k_selftest_wait<<<1, 32, 0, stream>>>(p);
+    return b200::check_launch("k_selftest_wait");
 }
 
 extern "C" int b200_nvfp4_device_status(unsigned int* out, int clear) {

@@ -37,6 +37,7 @@ constexpr int GX_THREADS = 384;
 constexpr int GX_MOVERS = 256;
 constexpr int GX_MAX_STEPS = 64;                   // K <= 16384
 constexpr int GX_MAX_STAGES = 8;
+constexpr int GX_MAX_SLABS = 16;                   // scale slabs per CTA (a slab covers 8 steps, or a whole tile when K/16 < 128)
 constexpr int GX_TMEM_COLS = 512;                  // accumulator [0, NT) | scale slots from column 256
 constexpr int GX_COL_SF = 256;
 constexpr uint32_t GX_A_BYTES = 16384;             // the MMA always reads 128 rows x 128 B of a stage
@@ -49,6 +50,8 @@ struct GxParams {
     unsigned int* status;
     int n_jobs, K, R, stages, prefetch_before_wait;
     int sc_box, sc_swz;
+    int T;                                         // consecutive weight-row tiles per CTA (T * NT <= 256 accumulator columns, T * K/256 <= 64 steps)
+    int sps, nslot;                                // steps per scale slab; slots of the slab ring
 };
 
 __device__ __forceinline__ void gx_tma_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
@@ -106,14 +109,14 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
     constexpr int SLOT = 16 + 4 * CBS;             // TMEM columns of one step's scales
     constexpr uint32_t AB_BYTES = GX_A_BYTES + NT * 128u;
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t full_bar[GX_MAX_STEPS], sf_bar[GX_MAX_STEPS], empty_bar[GX_MAX_STEPS], done_bar, sc_bar;
+    __shared__ uint64_t full_bar[GX_MAX_STEPS], sf_bar[GX_MAX_STEPS], empty_bar[GX_MAX_STEPS], slab_bar[GX_MAX_SLABS], done_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ float sx[NT];                       // 1 / (gs_w * gs_x[token]) of the job's rows
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, nst = K >> 8, R = p.R;
 
     GxJob J;
-    const int tile_n = (int)blockIdx.x / p.n_jobs, ji = (int)blockIdx.x - tile_n * p.n_jobs;
+    const int chunk = (int)blockIdx.x / p.n_jobs, ji = (int)blockIdx.x - chunk * p.n_jobs;
     const void* mw = &map_w;
     const void* ms = &map_s;
     if (p.table) {
@@ -128,21 +131,25 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         J.y += (size_t)J.row0 * J.ldy;
         J.gs_x += J.row0;
     }
-    const int rown0 = tile_n * R;                  // first weight row of the tile
-    if (rown0 >= J.N) return;
+    // this CTA's consecutive tiles of R weight rows: [tile0, tile0 + ntile)
+    const int tile0 = chunk * p.T, ntile = min(p.T, (J.N + R - 1) / R - tile0);
+    if (ntile <= 0) return;
+    const int nsteps = ntile * nst;                // step g: tile g / nst, 256-k block g % nst
+    const int sps = p.sps;                         // steps one scale slab covers; slab j = steps [j * sps, (j + 1) * sps)
+    const uint32_t slab_bytes = (uint32_t)R * (uint32_t)p.sc_box;
 
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
-    unsigned char* scl = ring + (size_t)p.stages * AB_BYTES;                    // the tile's weight scale rows: slabs [R x sc_box], 1 KB aligned (swizzle)
-    unsigned char* sfbs = scl + (size_t)R * (K >> 4);                           // per stage NT x 16 B of activation scales
+    unsigned char* scl = ring + (size_t)p.stages * AB_BYTES;                    // ring of weight-scale slabs [R x sc_box], 1 KB aligned (swizzle)
+    unsigned char* sfbs = scl + (size_t)p.nslot * slab_bytes;                   // per stage NT x 16 B of activation scales
 
     pdl_launch_dependents();
     if (warp >= 4) {
         const int i = tid - 128;
-        if (i < nst) mbar_init(smem_u32(&full_bar[i]), 1);
-        else if (i >= 64 && i < 64 + nst) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
-        else if (i >= 128 && i < 128 + nst) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
-        else if (i == 192) mbar_init(smem_u32(&done_bar), 1);
-        else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
+        if (i < nsteps) mbar_init(smem_u32(&full_bar[i]), 1);
+        else if (i >= 64 && i < 64 + nsteps) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
+        else if (i >= 128 && i < 128 + nsteps) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
+        else if (i >= 192 && i < 192 + GX_MAX_SLABS) mbar_init(smem_u32(&slab_bar[i - 192]), 1);
+        else if (i == 255) mbar_init(smem_u32(&done_bar), 1);
         mbar_fence_init();
     }
     if (warp == 2) {
@@ -155,34 +162,40 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
     const uint32_t tmem = tmem_base_s;
 
     if (warp == 0) {
-        // ---- TMA producer ----
+        // ---- TMA producer: lane l issues steps l, l + 32, .. (and the scale slab that starts with such a step) ----
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" :: "l"(mw) : "memory");
             asm volatile("prefetch.tensormap [%0];" :: "l"(ms) : "memory");
             asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
         }
         if (!p.prefetch_before_wait) pdl_wait();
-        const int nslab = (K >> 4) / p.sc_box;
-        if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), (uint32_t)R * (uint32_t)(K >> 4));
-        __syncwarp();
-        for (int q = lane; q < nslab; q += 32)
-            gx_tma_2d(smem_u32(scl) + (uint32_t)q * (uint32_t)R * (uint32_t)p.sc_box, ms, q * p.sc_box, rown0, smem_u32(&sc_bar));
-        const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+        const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), slab0 = smem_u32(&slab_bar[0]);
         const uint32_t step_bytes = (uint32_t)R * 128u + NT * 128u + NT * 16u;
-        for (int g = lane; g < nst; g += 32) {
+        int t = lane / nst, it = lane - t * nst;
+        for (int g = lane; g < nsteps; g += 32) {
+            const int rown0 = (tile0 + t) * R;
+            if (it % sps == 0) {
+                // the slab of scale rows that steps [g, g + sps) read; its slot is free once the MMAs of the
+                // last step of the slab that held it have completed (their scale movers are then done as well)
+                const int j = g / sps;
+                if (j >= p.nslot) mbar_wait_spin(empty0 + ((j - p.nslot + 1) * sps - 1) * 8, 0, p.status, 8);
+                mbar_expect_tx(slab0 + j * 8, slab_bytes);
+                gx_tma_2d(smem_u32(scl) + (uint32_t)(j % p.nslot) * slab_bytes, ms, (it / sps) * p.sc_box, rown0, slab0 + j * 8);
+            }
             const int s = g % p.stages;
             if (g >= p.stages) mbar_wait_spin(empty0 + (g - p.stages) * 8, 0, p.status, 9);
             const uint32_t bar = full0 + g * 8, dst = smem_u32(ring) + (uint32_t)s * AB_BYTES;
             mbar_expect_tx(bar, step_bytes);
-            gx_tma_2d(dst, mw, g * 128, rown0, bar);                              // weights may be read early (stable weights)
+            gx_tma_2d(dst, mw, it * 128, rown0, bar);                             // weights may be read early (stable weights)
             pdl_wait();                                                           // the activations come from the quantiser launch
-            gx_tma_2d(dst + GX_A_BYTES, &map_x, g * 128, J.row0, bar);
-            bulk_g2s(smem_u32(sfbs) + (uint32_t)s * NT * 16u, p.sfb + ((size_t)g * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
+            gx_tma_2d(dst + GX_A_BYTES, &map_x, it * 128, J.row0, bar);
+            bulk_g2s(smem_u32(sfbs) + (uint32_t)s * NT * 16u, p.sfb + ((size_t)it * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
+            it += 32; while (it >= nst) { it -= nst; ++t; }
         }
         __syncwarp();
         // The tcgen05.commit arrivals on empty_bar are asynchronous: wait for the last one of every
         // stage, or the CTA could exit with an arrival in flight that lands in the next CTA's shared memory.
-        for (int g = max(0, nst - p.stages) + lane; g < nst; g += 32)
+        for (int g = max(0, nsteps - p.stages) + lane; g < nsteps; g += 32)
             mbar_wait_spin(empty0 + g * 8, 0, p.status, 10);
         __syncwarp();
     } else if (warp == 1) {
@@ -190,8 +203,8 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
         const uint64_t dA0 = gx_desc(smem_u32(ring)), dB0 = gx_desc(smem_u32(ring) + GX_A_BYTES);
         const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-        int s = 0;
-        for (int g = 0; g < nst; ++g) {
+        int s = 0, t = 0, it = 0;
+        for (int g = 0; g < nsteps; ++g) {
             mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
             gx_fence_after();
             if (lane == 0) {
@@ -201,39 +214,43 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
                 for (int kb = 0; kb < 4; ++kb) {
                     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                  " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
-                                 :: "r"(tmem), "l"(dA0 + so + kb * 2), "l"(dB0 + so + kb * 2), "r"(idesc), "r"((uint32_t)((g | kb) != 0)),
-                                    "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
+                                 :: "r"(tmem + (uint32_t)(t * NT)), "l"(dA0 + so + kb * 2), "l"(dB0 + so + kb * 2), "r"(idesc),
+                                    "r"((uint32_t)((it | kb) != 0)), "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
                 }
                 gx_commit(empty0 + g * 8);
             }
             __syncwarp();
             if (++s == p.stages) s = 0;
+            if (++it == nst) { it = 0; ++t; }
         }
         if (lane == 0) gx_commit(smem_u32(&done_bar));
         __syncwarp();
     } else if (warp >= 4) {
         // ---- scale movers, then epilogue ----
-        const int t = tid - 128, grp = t >> 7, q4 = warp & 3;
+        const int tm = tid - 128, grp = tm >> 7, q4 = warp & 3;
         const uint32_t tq = tmem + ((uint32_t)(q4 * 32) << 16);
         pdl_wait();
-        if (t < NT) sx[t] = t < J.rows ? 1.0f / (J.gs_w[0] * J.gs_x[t]) : 0.f;
+        if (tm < NT) sx[tm] = tm < J.rows ? 1.0f / (J.gs_w[0] * J.gs_x[tm]) : 0.f;
         named_sync(1, GX_MOVERS);
-        const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
-        mbar_wait_spin(smem_u32(&sc_bar), 0, p.status, 12);
-        const int valid = J.N - rown0;               // weight rows of this tile that exist (may exceed R)
+        const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]), slab0 = smem_u32(&slab_bar[0]);
         int s = grp % p.stages;
-        for (int g = grp; g < nst; g += 2) {
+        int t = grp / nst, it = grp - t * nst;
+        for (int g = grp; g < nsteps; g += 2) {
+            const int j = g / sps, valid = J.N - (tile0 + t) * R;    // weight rows of this tile that exist (may exceed R)
+            mbar_wait_spin(slab0 + j * 8, 0, p.status, 12);
             mbar_wait_spin(full0 + g * 8, 0, p.status, 13);
             // weights: lane l holds rows l, l+32, l+64, l+96, 16 bytes each = four 64-k blocks x four scales;
             // block kb of row 32c + l goes to column kb*4 + c
+            const unsigned char* sl = scl + (size_t)(j % p.nslot) * slab_bytes;
+            const int is = it - (it / sps) * sps;                    // step within its slab
             uint32_t ra[16];
             #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int r = lane + 32 * c;
                 uint32_t off;
-                if (p.sc_swz) off = (uint32_t)(g >> 3) * (uint32_t)R * 128u + (uint32_t)r * 128u + (uint32_t)(((g & 7) ^ (r & 7)) << 4);
-                else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)g * 16u;
-                const uint4 v = (r < R && r < valid) ? *reinterpret_cast<const uint4*>(scl + off) : make_uint4(0u, 0u, 0u, 0u);
+                if (p.sc_swz) off = (uint32_t)r * 128u + (uint32_t)((is ^ (r & 7)) << 4);
+                else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)is * 16u;
+                const uint4 v = (r < R && r < valid) ? *reinterpret_cast<const uint4*>(sl + off) : make_uint4(0u, 0u, 0u, 0u);
                 ra[c] = v.x; ra[4 + c] = v.y; ra[8 + c] = v.z; ra[12 + c] = v.w;
             }
             // activations: lane l holds tokens l, l+32, ..; block kb of token 32c + l goes to column 16 + kb*CBS + c
@@ -251,25 +268,30 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             gx_fence_before();
             mbar_arrive(sf0 + g * 8);
             s += 2; while (s >= p.stages) s -= p.stages;
+            it += 2; while (it >= nst) { it -= nst; ++t; }
         }
-        // epilogue: group grp takes columns [grp * NT/2, (grp + 1) * NT/2)
+        // epilogue: group grp takes columns [grp * NT/2, (grp + 1) * NT/2) of every tile
         mbar_wait_spin(smem_u32(&done_bar), 0, p.status, 14);
         gx_fence_after();
-        const int r = q4 * 32 + lane, row = rown0 + r;
-        const bool ok = r < R && row < J.N;
+        const int r = q4 * 32 + lane;
         #pragma unroll 1
-        for (int c0 = grp * (NT / 2); c0 < (grp + 1) * (NT / 2); c0 += 16) {
-            if (c0 >= J.rows) break;                 // warp-uniform: the remaining tokens do not exist
-            uint32_t d[16];
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
-                           "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
-                         : "r"(tq + (uint32_t)c0));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (ok) {
-                #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c0 + j < J.rows) J.y[(size_t)(c0 + j) * J.ldy + row] = __uint_as_float(d[j]) * sx[c0 + j];
+        for (int te = 0; te < ntile; ++te) {
+            const int row = (tile0 + te) * R + r;
+            const bool ok = r < R && row < J.N;
+            #pragma unroll 1
+            for (int c0 = grp * (NT / 2); c0 < (grp + 1) * (NT / 2); c0 += 16) {
+                if (c0 >= J.rows) break;             // warp-uniform: the remaining tokens do not exist
+                uint32_t d[16];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
+                               "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+                             : "r"(tq + (uint32_t)(te * NT + c0)));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ok) {
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < J.rows) J.y[(size_t)(c0 + j) * J.ldy + row] = __uint_as_float(d[j]) * sx[c0 + j];
+                }
             }
         }
     }
@@ -289,7 +311,7 @@ __global__ void __launch_bounds__(256)
 k_quant_act(const void* __restrict__ xin, const void* __restrict__ xin2, float limit, const int* __restrict__ src_row,
             const int* __restrict__ m_dev, int M, int K, unsigned char* __restrict__ xq, unsigned char* __restrict__ sfb,
             size_t sfb_rows, float* __restrict__ gsx) {
-    __shared__ float red[8];
+    __shared__ uint32_t red[8];
     const int row = blockIdx.x, tid = threadIdx.x, groups = K >> 4;
     pdl_launch_dependents();
     pdl_wait();
@@ -327,20 +349,23 @@ k_quant_act(const void* __restrict__ xin, const void* __restrict__ xin2, float l
         }
     };
     float first[16];
-    float a = 0.f;
+    // maximum over the bit patterns of |x| (they order like the values; an infinity or a NaN wins instead of
+    // being dropped): a row that holds one gets a NaN global scale, and with it NaN outputs
+    uint32_t ai = 0u;
     for (int g = tid; g < groups; g += 256) {
         float v[16];
         load(g, v);
         #pragma unroll
-        for (int j = 0; j < 16; ++j) { a = fmaxf(a, fabsf(v[j])); if (g == tid) first[j] = v[j]; }
+        for (int j = 0; j < 16; ++j) { ai = max(ai, __float_as_uint(v[j]) & 0x7fffffffu); if (g == tid) first[j] = v[j]; }
     }
-    a = warp_max(a);
-    if ((tid & 31) == 0) red[tid >> 5] = a;
-    __syncthreads();
-    a = red[0];
     #pragma unroll
-    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
-    const float gs = nvfp4_global_scale(a);
+    for (int o = 16; o; o >>= 1) ai = max(ai, __shfl_xor_sync(0xffffffffu, ai, o));
+    if ((tid & 31) == 0) red[tid >> 5] = ai;
+    __syncthreads();
+    ai = red[0];
+    #pragma unroll
+    for (int w = 1; w < 8; ++w) ai = max(ai, red[w]);
+    const float gs = ai >= 0x7f800000u ? __uint_as_float(0x7fc00000u) : nvfp4_global_scale(__uint_as_float(ai));
     if (tid == 0) gsx[row] = gs;
     for (int g = tid; g < groups; g += 256) {
         float v[16];
@@ -405,14 +430,18 @@ static int gx_launch_t(GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw
     }
     const size_t static_smem = (size_t)ac[1] - 1;
     const size_t room = (size_t)ac[0] - static_smem - 2048;        // 1 KB alignment slack + 1 KB system reserve
-    const size_t fixed = (size_t)p.R * (p.K / 16);
+    const int nst = p.K / 256;
+    p.sps = p.sc_swz ? 8 : nst;
+    const int slabs = p.T * (nst / p.sps);
+    if (p.T < 1 || p.T * NT > GX_COL_SF || p.T * nst > GX_MAX_STEPS || slabs > GX_MAX_SLABS) return B200_ENOTIMPL;
+    p.nslot = std::min(slabs, 3);
+    const size_t fixed = (size_t)p.nslot * p.R * p.sc_box;
     const size_t per_stage = GX_A_BYTES + (size_t)NT * 128 + (size_t)NT * 16;
     if (fixed + 2 * per_stage > room) return B200_ENOTIMPL;
-    const int nst = p.K / 256;
     int stages = (int)std::min<size_t>((room - fixed) / per_stage, (size_t)GX_MAX_STAGES);
     stages = std::min(stages, (GX_TMEM_COLS - GX_COL_SF) / (16 + 4 * std::max(NT / 32, 4)));
-    stages = std::min(stages, nst);
-    if (stages < 2 && stages < nst) return B200_ENOTIMPL;
+    stages = std::min(stages, p.T * nst);
+    if (stages < 2 && stages < p.T * nst) return B200_ENOTIMPL;
     p.stages = stages;
     const size_t smem = (size_t)stages * per_stage + fixed + 1024;
     if (!ready[dev]) {
@@ -449,6 +478,19 @@ static int pick_nt(int M, int N) {
     return tiles_n * ((M + 127) / 128) <= nsm ? 128 : 256;
 }
 
+// Consecutive weight-row tiles per CTA: as many as the accumulator columns (T * NT <= 256), the per-step
+// barriers (T * K/256 <= 64) and the scale slabs allow while the launch still has a CTA for every SM.  A
+// CTA pays its set-up (TMEM, barriers, descriptors, pipeline fill and drain) once for all its tiles.
+static int pick_tiles_per_cta(int NT, int K, int tiles_n, long jobs) {
+    int box = 0, swz = 0;
+    scale_box(K, &box, &swz);
+    const int nst = K / 256, slabs_per_tile = swz ? nst / 8 : 1, nsm = sm_count();
+    int best = 1;
+    for (int T = 2; T <= tiles_n && T * NT <= GX_COL_SF && T * nst <= GX_MAX_STEPS && T * slabs_per_tile <= GX_MAX_SLABS; ++T)
+        if (jobs * ((tiles_n + T - 1) / T) >= nsm) best = T;
+    return best;
+}
+
 // Dense: y[M, N] = quant(x)[M, K] . W^T.  x_kind 0: bf16, 1: f32.  ws: gemm_mxf4_ws_bytes(M, K).
 int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s) {
     if (!y || !W || !W->packed || !W->scale || !W->gscale || !x || !ws || M < 1 || N < 1) return B200_EINVAL;
@@ -478,13 +520,15 @@ int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int
         !tmap_u8_2d(&mx, xq, (size_t)M, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
     if (int rc = quant_act_launch(x_kind ? 1 : 0, x, nullptr, 0.f, nullptr, nullptr, M, n_jobs * NT, K, xq, sfb, rows, gsx, s)) return rc;
     const int tiles_n = (N + R - 1) / R;
-    return gx_launch(NT, p, mx, mw, ms, tiles_n * n_jobs, s);
+    p.T = pick_tiles_per_cta(NT, K, tiles_n, n_jobs);
+    return gx_launch(NT, p, mx, mw, ms, (tiles_n + p.T - 1) / p.T * n_jobs, s);
 }
 
-// Jobs from a table in device memory (rows grouped by expert).  Every job's weight maps were encoded
+// Jobs from a table in device memory (rows grouped by expert); expected_jobs: how many of the max_jobs slots
+// are likely to hold a job (decides how many tiles a CTA takes).  Every job's weight maps were encoded
 // with box height R and N weight rows; the activation rows of all jobs live in one quantised buffer
 // (xq [x_rows, K/2], scales sfb [K/256][sfb_rows][16]).
-int gemm_mxf4_table(const GxJob* table, int max_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
+int gemm_mxf4_table(const GxJob* table, int max_jobs, long expected_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
                     const unsigned char* sfb, size_t sfb_rows, cudaStream_t s) {
     if (!gemm_mxf4_shape_ok(K)) return B200_ENOTIMPL;
     GxParams p{};
@@ -497,7 +541,8 @@ int gemm_mxf4_table(const GxJob* table, int max_jobs, int NT, int N, int K, int 
     CUtensorMap mx;
     if (!tmap_u8_2d(&mx, xq, x_rows, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
     const int tiles_n = (N + R - 1) / R;
-    return gx_launch(NT, p, mx, mx, mx, tiles_n * max_jobs, s);
+    p.T = pick_tiles_per_cta(NT, K, tiles_n, std::max(1L, expected_jobs));
+    return gx_launch(NT, p, mx, mx, mx, (tiles_n + p.T - 1) / p.T * max_jobs, s);
 }
 
 }  // namespace b200

@@ -66,25 +66,33 @@ __device__ __forceinline__ void stage_x(const float* __restrict__ x, int nrows, 
 // ---- R rows x M activation rows, one warp -----------------------------------------------------
 struct RowPtr { const uint8_t* p; const uint8_t* s; };
 
-template <int R>
+// ANY = false: rows are 16-byte aligned (packed) and 2-byte aligned (scales), checked by the host.
+// ANY = true: rows may sit at the format's floor -- packed bytes 4-byte aligned, scales at any address
+// (the reference guarantees no more: kernels/moe.cu:167-174) -- which only the device can see for expert
+// tables that live in device memory; the branch is warp-uniform and the values loaded are the same.
+template <int R, bool ANY = false>
 __device__ __forceinline__ void load_step(const RowPtr (&rows)[R], int c, uint4 (&w)[R], uint16_t (&s)[R]) {
     #pragma unroll
     for (int r = 0; r < R; ++r) {
-        w[r] = ldg_stream_v4(rows[r].p + (size_t)c * 16);
-        s[r] = ldg_stream_u16(rows[r].s + (size_t)c * 2);
+        const uint8_t* pp = rows[r].p + (size_t)c * 16;
+        const uint8_t* ps = rows[r].s + (size_t)c * 2;
+        if (!ANY || (((uintptr_t)pp & 15) == 0)) w[r] = ldg_stream_v4(pp);
+        else w[r] = make_uint4(ldg_stream_u32(pp), ldg_stream_u32(pp + 4), ldg_stream_u32(pp + 8), ldg_stream_u32(pp + 12));
+        if (!ANY || (((uintptr_t)ps & 1) == 0)) s[r] = ldg_stream_u16(ps);
+        else s[r] = (uint16_t)((uint32_t)__ldg(ps) | ((uint32_t)__ldg(ps + 1) << 8));
     }
 }
 
-template <int M, int R, int MATH>
+template <int M, int R, int MATH, bool ANY = false>
 __device__ __forceinline__ void warp_rows(const RowPtr (&rows)[R], int K, const uint4* xs,
                                           float (&acc)[R][M], int lane) {
     const int nch = K >> 5, stride = xs_chunks(K);
     uint4 wc[R]; uint16_t sc[R];
     int c = lane;
-    if (c < nch) load_step<R>(rows, c, wc, sc);
+    if (c < nch) load_step<R, ANY>(rows, c, wc, sc);
     for (; c < nch; c += 32) {
         uint4 wn[R]; uint16_t sn[R];
-        if (c + 32 < nch) load_step<R>(rows, c + 32, wn, sn);
+        if (c + 32 < nch) load_step<R, ANY>(rows, c + 32, wn, sn);
         #pragma unroll
         for (int m = 0; m < M; ++m) {
             uint32_t xr[16];
@@ -111,17 +119,17 @@ __device__ __forceinline__ void warp_rows(const RowPtr (&rows)[R], int K, const 
 // Same loop with a separate staged activation row per weight row (the MoE down projection,
 // where each slot's expert multiplies its own intermediate vector).  xr_base[r] points at the
 // staged row for weight row r.
-template <int R, int MATH>
+template <int R, int MATH, bool ANY = false>
 __device__ __forceinline__ void warp_rows_own_x(const RowPtr (&rows)[R], int K,
                                                 const uint4* const (&xr_base)[R], float (&acc)[R],
                                                 int lane) {
     const int nch = K >> 5;
     uint4 wc[R]; uint16_t sc[R];
     int c = lane;
-    if (c < nch) load_step<R>(rows, c, wc, sc);
+    if (c < nch) load_step<R, ANY>(rows, c, wc, sc);
     for (; c < nch; c += 32) {
         uint4 wn[R]; uint16_t sn[R];
-        if (c + 32 < nch) load_step<R>(rows, c + 32, wn, sn);
+        if (c + 32 < nch) load_step<R, ANY>(rows, c + 32, wn, sn);
         #pragma unroll
         for (int r = 0; r < R; ++r) {
             uint32_t xr[16];

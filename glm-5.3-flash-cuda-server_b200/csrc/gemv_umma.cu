@@ -76,14 +76,8 @@ struct UmParams {
     int T;                                         // consecutive row tiles of one job per CTA (T * max_m <= 8, T * K/256 <= 64)
     uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
     int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
-    unsigned long long* trace;                     // B200_TRACE builds only: 64 timestamps per CTA
 };
 
-#ifdef B200_TRACE
-#define UTRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = global_ns(); } while (0)
-#else
-#define UTRACE(slot) do { } while (0)
-#endif
 
 struct UmMaps { CUtensorMap w[B200_GEMV_MULTI_MAX]; CUtensorMap s[B200_GEMV_MULTI_MAX]; };
 
@@ -127,25 +121,32 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
     for (int m = 0; m < M; ++m) {
         const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
         const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
-        float a = 0.f;
+        // The maximum is taken over the bit patterns of |x|: they order like the values, and an infinity or
+        // a NaN (patterns from 0x7f800000 up) wins the maximum instead of being dropped as fmaxf would.
+        uint32_t a = 0u;
+        auto ab = [](float f) { return __float_as_uint(f) & 0x7fffffffu; };
         for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 v = ldx(xr, xr2, i + q);
                 if (SINGLE && i == t4 * 4) xv[q] = v;
-                a = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                a = max(a, max(max(ab(v.x), ab(v.y)), max(ab(v.z), ab(v.w))));
             }
         }
-        a = warp_max(a);
-        if (lane == 0) red[m][t4 >> 5] = a;
+        #pragma unroll
+        for (int o = 16; o; o >>= 1) a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+        if (lane == 0) red[m][t4 >> 5] = __uint_as_float(a);
     }
     named_sync(1, UM_WORKERS);
     // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
     auto row_inv = [&](int m) -> float {
-        float a = 0.f;
+        uint32_t ai = 0u;
         #pragma unroll
-        for (int w = 0; w < 8; ++w) a = fmaxf(a, red[m][w]);
-        const float gamma = (a > 0.f && a < 3.0e38f) ? a * (1.0f / 3.99f) : 1.f;
+        for (int w = 0; w < 8; ++w) ai = max(ai, __float_as_uint(red[m][w]));
+        const float a = __uint_as_float(ai);
+        // a row with an infinity or a NaN in it yields NaN for every output of that row (the fp32 kernels of
+        // the reference propagate non-finite activations too; digits cannot carry them)
+        const float gamma = ai >= 0x7f800000u ? __uint_as_float(0x7fc00000u) : (a > 0.f ? a * (1.0f / 3.99f) : 1.f);
         if (t4 < UM_NB) gam[m * UM_NB + t4] = gamma * __uint_as_float((uint32_t)(127 - 2 * t4) << 23);      // gamma * 4^-t
         return 16384.f / gamma;
     };
@@ -242,7 +243,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: per tile, slabs [R x sc_box]
 
     pdl_launch_dependents();
-    if (tid == 0) UTRACE(3);
     if (warp >= UM_LOAD_WARPS + UM_MMA_WARPS) {      // barrier init spread over the worker threads
         const int i = tid - UM_LOADERS - 32 * UM_MMA_WARPS;
         if (i < nsteps) mbar_init(smem_u32(&full_bar[i]), 1);
@@ -261,14 +261,13 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    if (tid == 0) UTRACE(4);
 
     if (warp < UM_LOAD_WARPS) {
         // ---- TMA producer: warp 0; lane l issues the loads of steps l, l + 32, ... ----
         // One thread issuing tensor loads back to back gets one out every ~0.35 us (measured), so
         // the steps are dealt to the lanes: each lane waits for its own stage and issues on its own.
         if (warp == 0) {
-            if (lane == 0) { UTRACE(0); asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
+            if (lane == 0) { asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
                              asm volatile("prefetch.tensormap [%0];" :: "l"(J.ms) : "memory"); }
             if (!p.prefetch_before_wait) pdl_wait();
             // All scale rows of the CTA first, in slabs [R rows x sc_box bytes]: one tensor load per
@@ -292,17 +291,14 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 const uint32_t bar = full0 + g * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
                 mbar_expect_tx(bar, bytes);
                 tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0 + t * p.R, bar);
-                if (g == 0) UTRACE(1);
             }
             __syncwarp();
-            if (lane == 0) UTRACE(2);
             // Tail: the tcgen05.commit arrivals on empty_bar are asynchronous.  Wait for the last one
             // of every stage, or the CTA could exit with an arrival still in flight and it would
             // land on whatever the next CTA keeps at that shared-memory address.
             for (int g = max(0, nsteps - p.stages) + lane; g < nsteps; g += 32)
                 UM_WAIT(empty0 + g * 8, 0, p.status, 5);
             __syncwarp();
-            if (lane == 0) UTRACE(62);
         }
         else if (warp == 1 && !GEN) {
             // L2 prefetch of the steps the ring cannot take at once (legal before the upstream kernel
@@ -320,7 +316,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         tc_fence_after();
         {
             const int me = warp - UM_LOAD_WARPS;
-            if (me == 0 && lane == 0) UTRACE(8);
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)M << 17) | ((128u >> 4) << 24);     // N = 8 M
             const uint64_t dA0 = umma_desc(smem_u32(ring), 1024, 2), dB0 = umma_desc(smem_u32(bimg), 1024, 2);
             const uint32_t tSB = tmem + UM_COL_SB;
@@ -345,7 +340,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                                         "r"(tsf + kb * 4), "r"(tSB) : "memory");
                     }
                     tc_commit(empty0 + g * 8);
-                    if (me == 0 && g < 16) UTRACE(9 + g / UM_MMA_WARPS);
                 }
                 __syncwarp();
                 s += UM_MMA_WARPS; while (s >= p.stages) s -= p.stages;
@@ -368,7 +362,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         if (!p.prefetch_before_wait) pdl_wait();
         const float gsv = J.gs[0];                       // weight data: with stable weights it may be read early
         pdl_wait();
-        if (t4 == 0) UTRACE(32);
         if (GEN && J.bimg) {
             // The B image was split once for all CTAs of the job by k_split_rows: copy it in.
             const uint32_t total = (uint32_t)nst * (uint32_t)p.max_m * 1024u;
@@ -383,7 +376,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         }
         fence_async_smem();
         tc_fence_before();
-        if (t4 == 0) UTRACE(33);
         named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // with the MMA warps
         {
             // Weight scales: the first four worker warps take the even steps, the other four the odd
@@ -425,7 +417,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(sf0 + g * 8);
-                if ((t4 & 127) == 0 && g < 24) UTRACE(34 + g);
                 s += 2; while (s >= p.stages) s -= p.stages;
                 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = vn[c];
@@ -435,7 +426,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // epilogue
             UM_WAIT(smem_u32(&done_bar), 0, p.status, 4);
             tc_fence_after();
-            if (t4 == 0) UTRACE(60);
             const int r = q4 * 32 + lane;
             for (int t = 0; t < T; ++t) {
                 const int row = row0 + t * p.R + r;
@@ -461,18 +451,13 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                     }
                 }
             }
-            if (t4 == 0) UTRACE(5);
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == UM_LOAD_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(UM_TMEM_COLS));
-    if (tid == 32 * UM_LOAD_WARPS) UTRACE(61);
 }
 
-#ifdef B200_TRACE
-unsigned long long* g_trace_umma = nullptr;
-#endif
 
 // Pre-split activations of a gemm: chunk c (rows 8c..8c+7) has its image at img + c * chunk_bytes
 // (rows at `stride`) and its digit weights at gam + c * 64.
@@ -629,12 +614,6 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     p.status = device_status_ptr();
     if (!p.status) return B200_ENOTIMPL;
     p.prefetch_before_wait = stable_weights_option();
-    p.trace = nullptr;
-#ifdef B200_TRACE
-    { static unsigned long long* tb = nullptr; static int cnt = 0;
-      if (!tb) { cudaMalloc(&tb, 8 * 1024 * 64 * 8); cudaMemset(tb, 0, 8 * 1024 * 64 * 8); }
-      p.trace = tb + (size_t)(cnt++ % 8) * 1024 * 64; g_trace_umma = tb; }
-#endif
     if (p.dry_run) return B200_OK;
     const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
     static bool ready_all[64][2] = {};               // the attribute is per device
@@ -703,10 +682,3 @@ int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float
 
 }  // namespace b200
 
-#ifdef B200_TRACE
-extern "C" int b200_debug_trace_umma(unsigned long long* host_out, int n_cta) {
-    if (!b200::g_trace_umma) return 1;    // all 8 launch regions of 1024 CTAs x 64 slots
-    (void)n_cta;
-    return cudaMemcpy(host_out, b200::g_trace_umma, (size_t)8 * 1024 * 64 * 8, cudaMemcpyDeviceToHost) != cudaSuccess;
-}
-#endif

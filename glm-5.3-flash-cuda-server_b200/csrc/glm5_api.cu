@@ -49,6 +49,18 @@ void gemm_multi_ws(const GemvJob* jobs, int n, int M, int K, int dtype, void* ws
     for (int i = 0; i < n; ++i) j[i] = b200_gemv_job{jobs[i].y, cw(jobs[i].W), jobs[i].x, jobs[i].N};
     must(b200_nvfp4_gemv_multi_ws(j, n, M, K, dtype, ws, s), "gemm_multi_ws");
 }
+void exact_prefill(bool on) { must(b200_nvfp4_set_option(B200_OPT_PREFILL_FP4, on ? 0 : 1), "exact_prefill"); }
+size_t gemm_bf16_workspace_bytes(int M, int K) { return b200_nvfp4_gemm_bf16_workspace_bytes(M, K); }
+void gemm_bf16(float* y, const WRef& W, const void* x_bf16, int M, int N, int K, void* ws, cudaStream_t s) {
+    const b200_wref w = cw(W);
+    must(b200_nvfp4_gemm_bf16(y, &w, x_bf16, M, N, K, ws, s), "gemm_bf16");
+}
+size_t dense_mlp_workspace_bytes(int M, int hidden, int inter) { return b200_dense_mlp_workspace_bytes(M, hidden, inter); }
+void dense_mlp_nvfp4(const float* x, const WRef& gate, const WRef& up, const WRef& down, int hidden, int inter,
+                     float limit, float* y, void* ws, int M, cudaStream_t s) {
+    const b200_wref g = cw(gate), u = cw(up), d = cw(down);
+    must(b200_dense_mlp(x, &g, &u, &d, hidden, inter, limit, y, ws, M, s), "dense_mlp_nvfp4");
+}
 void f32_to_bf16(void* dst, const float* src, size_t n, cudaStream_t s) { must(b200_f32_to_bf16(dst, src, n, s), "f32_to_bf16"); }
 void f32_from_bf16_dev(float* dst, const void* src, size_t n, cudaStream_t s) { must(b200_bf16_to_f32(dst, src, n, s), "f32_from_bf16_dev"); }
 
@@ -70,9 +82,11 @@ size_t moe_batch_workspace_floats(int M) {
 }
 size_t moe_workspace_floats() { return moe_batch_workspace_floats(1); }
 bool nvfp4_check_align(const Nvfp4Mat& m, const char* what) {
-    if (((uintptr_t)m.packed & 15) || ((uintptr_t)m.scale & 1) || ((uintptr_t)m.gscale & 3)) {
-        fprintf(stderr, "nvfp4: %s needs 16-byte aligned packed, 2-byte aligned scale, 4-byte aligned gscale "
-                        "(packed=%p scale=%p gscale=%p)\n", what, (const void*)m.packed, (const void*)m.scale, (const void*)m.gscale);
+    // the reference's floor (kernels/moe.cu:628-636): 4-byte aligned packed bytes and global scale; every kernel
+    // of this library runs from there (the 16-byte fast paths are chosen per tensor, on the device where needed)
+    if (((uintptr_t)m.packed & 3) || ((uintptr_t)m.gscale & 3)) {
+        fprintf(stderr, "nvfp4: %s needs 4-byte aligned packed bytes and global scale (packed=%p scale=%p gscale=%p)\n",
+                what, (const void*)m.packed, (const void*)m.scale, (const void*)m.gscale);
         return false;
     }
     return true;

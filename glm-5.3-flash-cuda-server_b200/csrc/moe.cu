@@ -108,7 +108,7 @@ k_expert_act(const __grid_constant__ MoeArgs a, int tiles, int total_tasks) {
         RowPtr rows[4] = {{G.packed + o0 * pr, G.scale + o0 * sr}, {U.packed + o0 * pr, U.scale + o0 * sr},
                           {G.packed + o1 * pr, G.scale + o1 * sr}, {U.packed + o1 * pr, U.scale + o1 * sr}};
         float acc[4][1] = {{0.f}, {0.f}, {0.f}, {0.f}};
-        warp_rows<1, 4, MATH>(rows, a.H, xs, acc, lane);
+        warp_rows<1, 4, MATH, true>(rows, a.H, xs, acc, lane);
         const float kg = inv_s[0] / G.gscale[0], ku = inv_s[0] / U.gscale[0];
         #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -161,7 +161,7 @@ k_expert_down(const __grid_constant__ MoeArgs a, int tiles, int total_tasks) {
                 coef[q] = (s0 + q < a.ns) ? w * inv_s[slot] / D.gscale[0] : 0.f;
             }
             float acc[3] = {0.f, 0.f, 0.f};
-            warp_rows_own_x<3, MATH>(rows, a.I, xb, acc, lane);
+            warp_rows_own_x<3, MATH, true>(rows, a.I, xb, acc, lane);
             tot = fmaf(acc[0], coef[0], tot);
             tot = fmaf(acc[1], coef[1], tot);
             tot = fmaf(acc[2], coef[2], tot);
@@ -196,9 +196,9 @@ static int grid_for(Kern kern, size_t smem, int tasks, int* grid) {
 }
 
 static int experts_forward(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
-                           const float* wts, float* act, int M, cudaStream_t s, bool allow_tensor_path, bool planned = false) {
-    if (allow_tensor_path) {                             // prepared layers, up to 8 tokens (moe_umma.cu)
-        const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s, planned);
+                           const float* wts, float* act, int M, cudaStream_t s, bool allow_tensor_path, bool planned = false, int wide = -1) {
+    if (allow_tensor_path) {                             // prepared layers (moe_umma.cu)
+        const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s, planned, wide);
         if (rc != B200_ENOTIMPL) return rc;
     }
     MoeArgs a{};
@@ -273,13 +273,18 @@ extern "C" int b200_moe_route(const float* x, const b200_moe_layer* L, int32_t* 
     return route_launch(x, L, sel, wts, logits, M, stream, MoePlan{});
 }
 
-extern "C" int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
-                                const float* wts, void* ws, int M, b200_stream stream) {
+int b200::moe_experts_mode(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                           void* ws, int M, cudaStream_t stream, int wide) {
     if (int rc = check_layer(L, M)) return rc;
     if (!x || !y || !sel || !wts || !ws) return B200_EINVAL;
     if ((uintptr_t)ws & 15) return B200_EALIGN;
     float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));
-    return experts_forward(x, L, y, sel, wts, act, M, stream, true);
+    return experts_forward(x, L, y, sel, wts, act, M, stream, true, false, wide);
+}
+
+extern "C" int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel,
+                                const float* wts, void* ws, int M, b200_stream stream) {
+    return moe_experts_mode(x, L, y, sel, wts, ws, M, stream, -1);
 }
 
 extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,

@@ -18,6 +18,7 @@
 // the slots in slot order.
 #include "b200_internal.h"
 #include "moe_plan.cuh"
+#include "tma_pipe.cuh"
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -37,14 +38,19 @@ struct Prepared {
 static std::vector<Prepared> g_prepared;
 static std::mutex g_prepared_mu;
 
-static const Prepared* find_prepared(const b200_moe_layer* L) {
+// A COPY of the layer's entry, taken under the lock (the table may grow or an entry be released by another
+// thread right after).  The device memory behind `maps` stays valid until b200_moe_release, which the
+// caller must not run while calls on that layer are still queued.
+static bool find_prepared(const b200_moe_layer* L, Prepared* out) {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
     std::lock_guard<std::mutex> lk(g_prepared_mu);
     for (const Prepared& p : g_prepared)
-        if (p.experts == L->experts && p.shared == L->shared && p.E == L->n_expert && p.H == L->hidden && p.I == L->inter && p.device == dev)
-            return &p;                                   // entries are never removed or moved while in use: see release
-    return nullptr;
+        if (p.maps && p.experts == L->experts && p.shared == L->shared && p.E == L->n_expert && p.H == L->hidden && p.I == L->inter && p.device == dev) {
+            if (out) *out = p;
+            return true;
+        }
+    return false;
 }
 
 // Box height for n_jobs jobs of N rows: fewest waves of CTAs over the SMs, each wave costing its
@@ -169,22 +175,24 @@ static int grouped_max_jobs(const b200_moe_layer* L, int M) { return (M * (L->to
 // Scratch of the tensor-core path behind the logits.  Up to 8 tokens: job tables | gate products |
 // up products | down products, one row per (token, slot) pair.  More: pair positions | job tables |
 // gathered activations | gate | up | down products, rows grouped by expert.
+static size_t moe_gx_ws_bytes(const b200_moe_layer* L, int M);
 size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
     const size_t ns = (size_t)L->topk + 1, pairs = (size_t)M * ns;
     if (M <= MU_MAX_TOKENS)
-        return up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4);
+        return std::max(moe_gx_ws_bytes(L, M), up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4));
     const size_t mj = (size_t)grouped_max_jobs(L, M);
-    return up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
+    return std::max(moe_gx_ws_bytes(L, M), up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
            up256(mj * (L->hidden >> 8) * 8192) + up256(mj * (L->inter >> 8) * 8192) +
-           2 * up256(pairs * L->hidden * 4) + 2 * up256(pairs * L->inter * 4);
+           2 * up256(pairs * L->hidden * 4) + 2 * up256(pairs * L->inter * 4));
 }
 
 // Fills `q` for a call on a prepared layer.  B200_ENOTIMPL: not prepared, too many tokens, or an
 // unaligned activation -> the caller runs the CUDA-core experts.
 int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, int M, MoePlan* q, int* R_gu, int* R_d) {
     if (M > MU_MAX_TOKENS || ((uintptr_t)x & 15)) return B200_ENOTIMPL;
-    const Prepared* P = find_prepared(L);
-    if (!P) return B200_ENOTIMPL;
+    Prepared Pc;
+    if (!find_prepared(L, &Pc)) return B200_ENOTIMPL;
+    const Prepared* P = &Pc;
     const int ns = L->topk + (L->shared ? 1 : 0), pairs = M * ns, H = L->hidden, I = L->inter;
     char* w = static_cast<char*>(scratch);
     q->j1 = reinterpret_cast<UmJob*>(w);
@@ -203,8 +211,9 @@ int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, i
 static int moe_umma_grouped(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
                             void* scratch, int M, cudaStream_t s) {
     if (((uintptr_t)x & 15) || L->n_expert + 1 > MG_MAX_GROUPS) return B200_ENOTIMPL;
-    const Prepared* P = find_prepared(L);
-    if (!P) return B200_ENOTIMPL;
+    Prepared Pc;
+    if (!find_prepared(L, &Pc)) return B200_ENOTIMPL;
+    const Prepared* P = &Pc;
     const int ns = L->topk + (L->shared ? 1 : 0), pairs = M * ns, H = L->hidden, I = L->inter;
     const int max_jobs = grouped_max_jobs(L, M);
     const size_t np = (size_t)M * (L->topk + 1);     // the sizes the workspace was laid out with
@@ -238,9 +247,117 @@ static int moe_umma_grouped(const float* x, const b200_moe_layer* L, float* y, c
     return check_launch("k_moe_combine");
 }
 
+// ---- 16 tokens and more: rows grouped by expert, both GEMM operands in NVFP4 -----------------------
+// Same counting sort as k_moe_group, but the jobs are those of the wide GEMM (gemm_mxf4.cu): one job
+// per expert and chunk of up to NT rows, so that an expert's weights are read once per NT rows that
+// chose it (the passes of 8 rows above re-read them NT/8 times).  src_row[pos] = token of the pair
+// sorted to position pos: the activation quantiser gathers with it.
+__global__ void __launch_bounds__(1024)
+k_moe_group_gx(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int* __restrict__ posof,
+               int* __restrict__ src_row, GxJob* __restrict__ j1, GxJob* __restrict__ j2,
+               const float* __restrict__ gsx1, const float* __restrict__ gsx2, int M, int NT, int max_jobs) {
+    __shared__ int cnt[MG_MAX_GROUPS], off[MG_MAX_GROUPS], jstart[MG_MAX_GROUPS], cursor[MG_MAX_GROUPS];
+    __shared__ int total_jobs;
+    pdl_wait();
+    const int G = q.E + 1, pairs = M * q.ns;
+    for (int e = threadIdx.x; e < G; e += blockDim.x) { cnt[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    auto group_of = [&](int p) {
+        const int m = p / q.ns, slot = p - m * q.ns;
+        if (slot >= q.topk) return q.E;
+        const int e = sel[(size_t)m * q.topk + slot];
+        return e < 0 ? 0 : (e >= q.E ? q.E - 1 : e);
+    };
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[group_of(p)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, j = 0;
+        for (int e = 0; e < G; ++e) { off[e] = o; jstart[e] = j; o += cnt[e]; j += (cnt[e] + NT - 1) / NT; }
+        total_jobs = j;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = group_of(p), pos = off[e] + atomicAdd(&cursor[e], 1);
+        posof[p] = pos;
+        src_row[pos] = p / q.ns;
+    }
+    for (int e = threadIdx.x; e < G; e += blockDim.x) {
+        const b200_nvfp4_mat* mats = e < q.E ? q.experts + (size_t)e * 3 : q.shared;
+        const unsigned char* mp = q.maps + (size_t)e * 6 * 128;
+        for (int c = 0; c * NT < cnt[e]; ++c) {
+            const int idx = jstart[e] + c, rows = min(NT, cnt[e] - NT * c), pos0 = off[e] + NT * c;
+            j1[2 * idx] = GxJob{q.gbuf + (size_t)pos0 * q.I, mats[0].gscale, gsx1 + pos0, mp, mp + 128, pos0, rows, q.I, q.I};
+            j1[2 * idx + 1] = GxJob{q.ubuf + (size_t)pos0 * q.I, mats[1].gscale, gsx1 + pos0, mp + 256, mp + 384, pos0, rows, q.I, q.I};
+            j2[idx] = GxJob{q.part + (size_t)pos0 * q.H, mats[2].gscale, gsx2 + pos0, mp + 512, mp + 640, pos0, rows, q.H, q.H};
+        }
+    }
+    for (int idx = total_jobs + threadIdx.x; idx < max_jobs; idx += blockDim.x) {
+        const GxJob none{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+        j1[2 * idx] = none; j1[2 * idx + 1] = none; j2[idx] = none;
+    }
+}
+
+// Token tile of the grouped wide GEMM: narrow while few rows share an expert (a job's cost is its
+// expert's weights whatever its width, and narrow tiles keep more stages in flight).
+static int gx_tile(int M) { return M <= 64 ? 32 : (M <= 256 ? 64 : 128); }
+static int gx_max_jobs(const b200_moe_layer* L, int M) { return (M * (L->topk + 1)) / gx_tile(M) + L->n_expert + 1; }
+
+static size_t moe_gx_ws_bytes(const b200_moe_layer* L, int M) {
+    const size_t np = (size_t)M * (L->topk + 1), mj = (size_t)gx_max_jobs(L, M), padrows = np + 256;
+    const size_t H = L->hidden, I = L->inter;
+    return 2 * up256(np * 4) + up256(mj * 3 * sizeof(GxJob)) +
+           up256(np * (H / 2)) + up256(padrows * (H / 16)) + up256(np * 4) +          // quantised token rows
+           up256(np * (I / 2)) + up256(padrows * (I / 16)) + up256(np * 4) +          // quantised SwiGLU rows
+           2 * up256(np * I * 4) + up256(np * H * 4);                                 // gate, up, down products
+}
+
+static int moe_gx_grouped(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
+                          void* scratch, int M, cudaStream_t s) {
+    if (((uintptr_t)x & 15) || L->n_expert + 1 > MG_MAX_GROUPS || !gemm_mxf4_shape_ok(L->hidden) || !gemm_mxf4_shape_ok(L->inter)) return B200_ENOTIMPL;
+    Prepared Pc;
+    if (!find_prepared(L, &Pc)) return B200_ENOTIMPL;
+    const Prepared* P = &Pc;
+    const int ns = L->topk + (L->shared ? 1 : 0), pairs = M * ns, H = L->hidden, I = L->inter;
+    const int NT = gx_tile(M), max_jobs = gx_max_jobs(L, M);
+    const size_t np = (size_t)M * (L->topk + 1), padrows = np + 256;
+    char* w = static_cast<char*>(scratch);
+    int* posof = reinterpret_cast<int*>(w); w += up256(np * 4);
+    int* src_row = reinterpret_cast<int*>(w); w += up256(np * 4);
+    GxJob* j1 = reinterpret_cast<GxJob*>(w); GxJob* j2 = j1 + (size_t)2 * max_jobs; w += up256((size_t)max_jobs * 3 * sizeof(GxJob));
+    unsigned char* xq1 = reinterpret_cast<unsigned char*>(w); w += up256(np * (H / 2));
+    unsigned char* sf1 = reinterpret_cast<unsigned char*>(w); w += up256(padrows * (H / 16));
+    float* gs1 = reinterpret_cast<float*>(w); w += up256(np * 4);
+    unsigned char* xq2 = reinterpret_cast<unsigned char*>(w); w += up256(np * (I / 2));
+    unsigned char* sf2 = reinterpret_cast<unsigned char*>(w); w += up256(padrows * (I / 16));
+    float* gs2 = reinterpret_cast<float*>(w); w += up256(np * 4);
+    MoePlan q{};
+    q.gbuf = reinterpret_cast<float*>(w); w += up256(np * I * 4);
+    q.ubuf = reinterpret_cast<float*>(w); w += up256(np * I * 4);
+    q.part = reinterpret_cast<float*>(w);
+    q.experts = L->experts; q.shared = L->shared; q.maps = P->maps; q.x = x;
+    q.topk = L->topk; q.ns = ns; q.E = L->n_expert; q.H = H; q.I = I;
+    k_moe_group_gx<<<1, 1024, 0, s>>>(q, sel, posof, src_row, j1, j2, gs1, gs2, M, NT, max_jobs);
+    if (int rc = check_launch("k_moe_group_gx")) return rc;
+    if (int rc = quant_act_launch(1, x, nullptr, 0.f, src_row, nullptr, pairs, pairs, H, xq1, sf1, padrows, gs1, s)) return rc;
+    // jobs the table is likely to hold: every expert that can be hit once, plus the extra chunks of busy experts
+    const long expect = std::min<long>(L->n_expert, (long)M * L->topk) + (L->shared ? 1 : 0) + pairs / NT;
+    if (int rc = gemm_mxf4_table(j1, 2 * max_jobs, 2 * expect, NT, I, H, P->R_gu, xq1, (size_t)pairs, sf1, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = quant_act_launch(2, q.gbuf, q.ubuf, L->swiglu_limit, nullptr, nullptr, pairs, pairs, I, xq2, sf2, padrows, gs2, s)) return rc;
+    if (int rc = gemm_mxf4_table(j2, max_jobs, expect, NT, H, I, P->R_d, xq2, (size_t)pairs, sf2, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    const int y4 = M * (H >> 2);
+    k_moe_combine<<<(y4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, posof, M, q.topk, ns, H);
+    return check_launch("k_moe_combine");
+}
+
 // The experts of a call on a prepared layer.  planned: the job tables were already written (by the router).
 int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
-                     void* scratch, int M, cudaStream_t s, bool planned) {
+                     void* scratch, int M, cudaStream_t s, bool planned, int wide) {
+    // wide: 1 = the grouped wide GEMM whatever M, 0 = never, -1 = by this call's row count
+    if (wide < 0) wide = M >= PREFILL_MIN_ROWS && prefill_fp4_option();
+    if (wide) {                                                    // prefill widths: an expert's weights once per up to 128 rows
+        const int rc = moe_gx_grouped(x, L, y, sel, wts, scratch, M, s);
+        if (rc != B200_ENOTIMPL) return rc;
+    }
     if (M > MU_MAX_TOKENS) return moe_umma_grouped(x, L, y, sel, wts, scratch, M, s);
     MoePlan q{};
     int R_gu = 0, R_d = 0;
@@ -263,7 +380,7 @@ using namespace b200;
 
 extern "C" int b200_moe_prepare(const b200_moe_layer* L) {
     if (!L || !L->experts || L->n_expert < 1 || L->hidden <= 0 || L->inter <= 0) return B200_EINVAL;
-    if (find_prepared(L)) return B200_OK;
+    if (find_prepared(L, nullptr)) return B200_OK;
     if (!umma_shape_ok(L->hidden) || !umma_shape_ok(L->inter) || (L->hidden & 3)) return B200_ENOTIMPL;
     const int E = L->n_expert, nexp = E + 1;
     std::vector<b200_nvfp4_mat> mats((size_t)nexp * 3);
@@ -292,8 +409,8 @@ extern "C" int b200_moe_prepare(const b200_moe_layer* L) {
     if (cudaMalloc(&P.maps, host.size()) != cudaSuccess) return launch_failed("moe_prepare: cudaMalloc");
     if (cudaMemcpy(P.maps, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(P.maps); return launch_failed("moe_prepare: upload"); }
     std::lock_guard<std::mutex> lk(g_prepared_mu);
-    g_prepared.reserve(4096);                            // pointers into the vector stay valid
-    if (g_prepared.size() >= 4096) { cudaFree(P.maps); return B200_ELIMIT; }
+    for (Prepared& q : g_prepared)
+        if (!q.maps) { q = P; return B200_OK; }          // a released slot
     g_prepared.push_back(P);
     return B200_OK;
 }
@@ -305,7 +422,8 @@ extern "C" int b200_moe_release(const b200_moe_layer* L) {
     std::lock_guard<std::mutex> lk(g_prepared_mu);
     for (Prepared& p : g_prepared)
         if (p.experts == L->experts && p.shared == L->shared && p.device == dev && p.maps) {
-            cudaFree(p.maps); p.maps = nullptr; p.experts = nullptr; p.shared = nullptr; p.E = -1;   // slot stays, never matches again
+            cudaFree(p.maps);                            // waits for the device: queued launches on this layer have finished
+            p.maps = nullptr; p.experts = nullptr; p.shared = nullptr; p.E = -1;   // the slot is free for the next prepare
             return B200_OK;
         }
     return B200_EINVAL;

@@ -1,10 +1,9 @@
-"""GPU side of the expert-parallel MoE layer: this rank's expert shard as library objects, and the
-three closures ExpertParallelMoE needs (route / compute / shared), all of them calls into
-libb200nvfp4.so.  Weights are seeded per global expert id, so every world size sees the same
-model and EP(G) can be checked against EP(1)."""
+"""Test and benchmark plumbing for the expert-parallel MoE layer: builds this rank's shard of a seeded
+layer as library objects and opens the library's expert-parallel context (b200_ep_*, C++ + NCCL inside
+libb200nvfp4.so) on it.  Nothing here computes or communicates; weights are seeded per global expert
+id, so every world size sees the same model and EP(G) can be checked against EP(1)."""
 import torch
 from . import binding as B
-from .ep import ExpertParallelMoE
 
 
 def expert_weights(seed, layer, e, H, I, device):
@@ -24,11 +23,21 @@ def router_weights(seed, layer, E, H, device):
     return router, bias
 
 
+def shared_unique_id(rank, world):
+    """One NCCL unique id made on rank 0 and handed to every rank over torch.distributed."""
+    if world == 1:
+        return None
+    import torch.distributed as dist
+    box = [B.ep_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
 class RankLayer:
     """One MoE layer as rank `rank` of `world` holds it: router + bias + shared expert replicated,
-    experts [rank*E/world, (rank+1)*E/world) local."""
+    experts [rank*E/world, (rank+1)*E/world) local; `ctx` is the library's expert-parallel context."""
 
-    def __init__(self, seed, layer, E, topk, H, I, rank, world, device, group=None, popularity_bias=None):
+    def __init__(self, seed, layer, E, topk, H, I, rank, world, device, max_tokens, popularity_bias=None):
         self.E, self.topk, self.H, self.I = E, topk, H, I
         epr = E // world
         self.router, self.bias = router_weights(seed, layer, E, H, device)
@@ -36,38 +45,26 @@ class RankLayer:
             self.bias = self.bias + popularity_bias.to(device)
         self.local = [expert_weights(seed, layer, rank * epr + j, H, I, device) for j in range(epr)]
         self.shared_w = expert_weights(seed, layer, E, H, I, device)
-        # three views of the same weights for the three library calls
+        # three views of the same weights for the library: the router over all E experts (its expert table is
+        # never read), the local shard as a layer with topk = 1, the shared expert as a one-expert layer
         self.l_route = B.MoeLayer(self.router, self.bias, self.local, None, topk, H, I)
-        self.l_route.c.n_expert = E                       # the router ranks all E experts; no expert is touched
+        self.l_route.c.n_expert = E
         self.l_route.n_expert = E
         self.l_local = B.MoeLayer(self.router, self.bias, self.local, None, 1, H, I)
         self.l_shared = B.MoeLayer(self.router, self.bias, [self.shared_w], None, 1, H, I)
-        # descriptors for the tensor-core experts (rows grouped by local expert); False = geometry unsuitable
         self.tensor_core = B.moe_prepare(self.l_local) and B.moe_prepare(self.l_shared)
-        self.ep = ExpertParallelMoE(E, topk, H, self.route, self.compute, self.shared, group)
+        self.ctx = B.EpContext(self.l_route, self.l_local, self.l_shared, rank, world, max_tokens, shared_unique_id(rank, world))
         self.expert_bytes = 3 * (I * H // 2 + I * H // 16 + 4)
 
-    def route(self, x):
-        sel, wts, _ = B.moe_route(self.l_route, x)
-        return sel, wts
+    def forward(self, x, y=None, sel=None, wts=None):
+        return self.ctx.forward(x, y, sel, wts)
 
-    def compute(self, rows, eid):
-        R = rows.shape[0]
-        ones = torch.ones((R, 1), dtype=torch.float32, device=rows.device)
-        return B.moe_experts(self.l_local, rows.contiguous(), eid.view(R, 1).contiguous(), ones)
+    def step_bytes(self, T_local, stats):
+        """Algorithmic bytes of a forward on this rank: local expert weights touched once each + the
+        shared expert, router, local tokens in and out, dispatched rows in (bf16) and out (f32)."""
+        return ((stats['local_experts_touched'] + 1) * self.expert_bytes + self.E * self.H * 2 + self.E * 4
+                + 2 * T_local * self.H * 4 + stats['recv_rows'] * self.H * 6)
 
-    def shared(self, x):
-        T = x.shape[0]
-        z = torch.zeros((T, 1), dtype=torch.int32, device=x.device)
-        ones = torch.ones((T, 1), dtype=torch.float32, device=x.device)
-        return B.moe_experts(self.l_shared, x, z, ones)
-
-    def forward(self, x):
-        return self.ep.forward(x)
-
-    def step_bytes(self, T_local):
-        """Algorithmic bytes of the last forward on this rank: expert weights touched once each,
-        router, local tokens in and out, dispatched rows in and out."""
-        s = self.ep.last_stats
-        return ((s['local_experts_touched'] + 1) * self.expert_bytes + self.E * self.H * 2 + self.E * 4
-                + 2 * T_local * self.H * 4 + 2 * s['recv_rows'] * self.H * 4)
+    def close(self):
+        self.ctx.close()
+        B.moe_release(self.l_local); B.moe_release(self.l_shared)

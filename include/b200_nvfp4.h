@@ -29,7 +29,9 @@ enum {
     B200_EALIGN = 3,      /* pointer below the 4-byte floor the format guarantees */
     B200_ELAUNCH = 4,     /* the CUDA runtime refused the launch (cudaGetLastError text logged) */
     B200_ELIMIT = 5,      /* size beyond a documented maximum */
-    B200_ENOTIMPL = 6
+    B200_ENOTIMPL = 6,
+    B200_ETIMEOUT = 7,    /* a bounded host-side wait ran out (expert-parallel exchange) */
+    B200_ECOMM = 8        /* NCCL is missing or returned an error */
 };
 enum { B200_F32 = 0, B200_BF16 = 1 };          /* dtype of a non-quantised weight (gemv.h:13) */
 enum { B200_GEMV_MULTI_MAX = 8, B200_GEMV_M_MAX = 8 };
@@ -59,7 +61,11 @@ typedef struct {
     const float*   gscale;
 } b200_nvfp4_mat;
 
-/* Mirrors glm5::MoeLayer (reference include/moe.h:19-26) plus the geometry the reference
+/* Alignment of an expert's tensors: packed bytes and gscale 4-byte aligned (the floor the reference's
+ * checkpoint guarantees, kernels/moe.cu:167-174, 628-636), scales at any address.  The CUDA-core expert
+ * kernels take 16-byte loads where a tensor allows it and 4-byte loads where not; b200_moe_prepare (the
+ * tensor-core experts) wants every tensor 16-byte aligned and answers B200_ENOTIMPL otherwise.
+ * Mirrors glm5::MoeLayer (reference include/moe.h:19-26) plus the geometry the reference
  * bakes in at compile time (include/glm5_config.h:20, 84-91), here per layer at run time. */
 typedef struct {
     b200_wref             router_w;      /* bf16 [n_expert, hidden] */
@@ -84,6 +90,11 @@ int         b200_nvfp4_version(void);
  * word into *out (host pointer; 0 = nothing happened) and optionally clears it.  No counterpart
  * in the reference, whose kernels never wait on one another. */
 int b200_nvfp4_device_status(unsigned int* out, int clear);
+
+/* Self-test of that mechanism: enqueues one small kernel whose only thread waits on a barrier nobody
+ * arrives at.  The wait runs out after its limit (about a second), the kernel returns normally, and
+ * b200_nvfp4_device_status then reports site 15 (0x000f0000 | block 0).  The context stays usable. */
+int b200_nvfp4_selftest_bounded_wait(b200_stream stream);
 
 /* Process-wide options.  B200_OPT_STABLE_WEIGHTS = 1 declares that no kernel running on a
  * stream writes NVFP4 weight buffers that a later call on that stream reads (true for an
@@ -154,6 +165,16 @@ int b200_nvfp4_gemm_bf16(float* y, const b200_wref* W, const void* x_bf16, int M
 int b200_nvfp4_quantize_tokens(const void* x, int x_is_f32, int M, int K, uint8_t* packed,
                                uint8_t* scale_step_major, float* gs, b200_stream stream);
 
+/* The dense-layer MLP in one call: y[M,hidden] = down . ( silu(min(gate.x, limit)) * clamp(up.x, -limit, limit) ).
+ * Replaces glm5::dense_mlp / dense_mlp_batch (reference kernels/layer.cu:235-254, k_swiglu_clamped :201-208).
+ * gate, up: NVFP4 [inter, hidden]; down: NVFP4 [hidden, inter].  gate and up run as one fused two-job launch up
+ * to 8 rows; from 16 rows on the products follow b200_nvfp4_gemm_ws (wide GEMM unless B200_OPT_PREFILL_FP4 is 0).
+ * ws: b200_dense_mlp_workspace_bytes(M, hidden, inter) bytes, 256-byte aligned (the reference's caller passes
+ * 2 * M * inter floats; this needs the split scratch as well). */
+size_t b200_dense_mlp_workspace_bytes(int M, int hidden, int inter);
+int b200_dense_mlp(const float* x, const b200_wref* gate, const b200_wref* up, const b200_wref* down,
+                   int hidden, int inter, float limit, float* y, void* ws, int M, b200_stream stream);
+
 /* Element-wise converters (reference include/gemv.h:61-62, kernels/gemv.cu:470-488). */
 int b200_f32_to_bf16(void* dst_bf16, const float* src, size_t n, b200_stream stream);
 int b200_bf16_to_f32(float* dst, const void* src_bf16, size_t n, b200_stream stream);
@@ -218,6 +239,43 @@ int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const in
 size_t b200_moe_static_ws_limit(void);
 int b200_moe_forward_static(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
                             float* wts, int M, b200_stream stream);
+
+/* ---- expert-parallel MoE layer (one process per GPU, NCCL) ------------------------------------
+ * The reference has no multi-GPU form (all experts sit behind one device table, src/engine.cu:168-195);
+ * this is the same block (kernels/moe.cu:669-740, fixed-order gate sum :584-597) with the experts of a
+ * layer sharded over `world` GPUs of one node: rank r owns experts [r*E/world, (r+1)*E/world), router,
+ * bias and shared expert are replicated, tokens are data-parallel.  Per call: route, one NCCL
+ * all-gather of the per-destination counts, ONE grouped ncclSend/ncclRecv round that carries token rows
+ * (bf16) and expert ids in the same message, the local experts on the received rows, one reverse round
+ * with the f32 output rows, and the gate-weighted sum in slot order plus the shared expert (which runs on
+ * a second stream and overlaps the exchange).  Token rows travel as bf16: a token's expert inputs are
+ * its values rounded to bf16.
+ *
+ * b200_ep_unique_id: rank 0 fills 128 bytes (HOST) that the caller hands to every rank by its own means.
+ * b200_ep_create: allocates the context's device buffers for up to max_tokens local tokens per call
+ *   (worst case: every pair of every rank lands on this rank) and joins the NCCL communicator (a
+ *   collective call: every rank must make it).  `router`: the layer's router and bias over ALL E experts
+ *   (its expert tables are never read); `local`: this rank's E/world experts as a layer with topk = 1
+ *   (call b200_moe_prepare on it first to get the tensor-core experts); `shared`: one expert, topk = 1,
+ *   or NULL.  The tables and weights must outlive the context.  world == 1 needs no NCCL and no id.
+ * b200_ep_forward: x, y [T, hidden] f32, sel/wts [T, topk] outputs, all on this rank.  With world > 1 the
+ *   call waits on the host (bounded, 20 s) for the exchange sizes, so it cannot be captured in a CUDA
+ *   graph; B200_ETIMEOUT means a peer never joined, and the communicator has been aborted.
+ * libnccl.so.2 is bound at run time, on the first context with world > 1. */
+typedef struct b200_ep b200_ep;
+typedef struct {
+    int tokens, recv_rows, sent_remote_rows, recv_remote_rows, local_experts_touched, pad;
+    unsigned long long dispatch_bytes_out, combine_bytes_in;      /* bytes that crossed NVLink for this rank's tokens */
+    float plan_us, dispatch_us, experts_us, combine_us, total_us; /* device time of the last call's phases (CUDA events) */
+    float pad2;
+} b200_ep_stats;
+int b200_ep_unique_id(void* id128);
+int b200_ep_create(b200_ep** out, const void* id128, int rank, int world, const b200_moe_layer* router,
+                   const b200_moe_layer* local, const b200_moe_layer* shared, int max_tokens);
+int b200_ep_forward(b200_ep* ep, const float* x, float* y, int32_t* sel, float* wts, int T,
+                    b200_stream stream);
+int b200_ep_last_stats(const b200_ep* ep, b200_ep_stats* out);     /* synchronises the device */
+int b200_ep_destroy(b200_ep* ep);
 
 #ifdef __cplusplus
 }

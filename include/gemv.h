@@ -49,9 +49,21 @@ void gemm_multi(const GemvJob* jobs, int n, int M, int K, int dtype, cudaStream_
 // rows are then prepared for the tensor cores once per call instead of once per thread block:
 // from 3 rows on this is faster (8 rows: 18 us instead of 26 us for the six sibling products; a
 // 128-row prefill chunk: 2.2x), and the results are the same bits.
+// From 16 rows on gemm_ws runs the wide tensor-core GEMM (weights read once per 256 rows, activations
+// quantised to NVFP4 per token: a few per cent from the exact product) unless exact_prefill(true) was called.
 size_t split_workspace_bytes(int M, int K);
 void gemm_ws(float* y, const WRef& W, const float* x, int M, int N, int K, int dtype, void* ws, cudaStream_t s);
 void gemm_multi_ws(const GemvJob* jobs, int n, int M, int K, int dtype, void* ws, cudaStream_t s);
+void exact_prefill(bool on);
+// Not in the reference: the wide GEMM on bf16 activations, y[M,N] f32 = x[M,K] bf16 . W^T (W NVFP4);
+// ws = gemm_bf16_workspace_bytes(M, K) bytes.
+size_t gemm_bf16_workspace_bytes(int M, int K);
+void gemm_bf16(float* y, const WRef& W, const void* x_bf16, int M, int N, int K, void* ws, cudaStream_t s);
+// The dense-layer MLP (reference kernels/layer.cu:235-254) on NVFP4 weights gate, up [inter, hidden] and
+// down [hidden, inter]: ws = dense_mlp_workspace_bytes(M, hidden, inter) bytes.
+size_t dense_mlp_workspace_bytes(int M, int hidden, int inter);
+void dense_mlp_nvfp4(const float* x, const WRef& gate, const WRef& up, const WRef& down, int hidden, int inter,
+                     float limit, float* y, void* ws, int M, cudaStream_t s);
 
 void f32_to_bf16(void* dst, const float* src, size_t n, cudaStream_t s);
 void f32_from_bf16_dev(float* dst, const void* src, size_t n, cudaStream_t s);

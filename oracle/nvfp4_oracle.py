@@ -234,6 +234,32 @@ def moe_experts(x, sel, wts, experts, shared, limit=SWIGLU_LIMIT):
     return y
 
 
+def moe_experts_act_nvfp4(x, sel, wts, experts, shared, limit=SWIGLU_LIMIT):
+    """The expert half of the block as the wide tensor-core path computes it: the same SwiGLU experts
+    (reference ref/gen_moe.py:79-96) with both operands of every product in NVFP4 -- the token row is
+    quantised per token before gate/up (gemm_act_nvfp4), and the SwiGLU output (rounded to fp32) is
+    quantised per row again before the down projection.  Rows are processed per distinct expert."""
+    x = np.atleast_2d(np.asarray(x, np.float32))
+    M, H = x.shape
+    y = np.zeros((M, H), np.float64)
+    xq = dequant_rows(*quantize_rows(x)).astype(np.float64)
+
+    def mlp(rows, gate, up, down):
+        g = np.minimum(rows @ dequant(*gate).astype(np.float64).T, limit)
+        u = np.clip(rows @ dequant(*up).astype(np.float64).T, -limit, limit)
+        act = ((g / (1.0 + np.exp(-g))) * u).astype(np.float32)
+        aq = dequant_rows(*quantize_rows(act)).astype(np.float64)
+        return aq @ dequant(*down).astype(np.float64).T
+
+    sel = np.asarray(sel)
+    for e in sorted(set(sel.ravel().tolist())):
+        tok, slot = np.nonzero(sel == e)
+        y[tok] += mlp(xq[tok], *experts[e]) * np.asarray(wts, np.float64)[tok, slot][:, None]
+    if shared is not None:
+        y += mlp(xq, *shared)
+    return y
+
+
 def rel_l2(a, b):
     a = np.asarray(a, np.float64).ravel(); b = np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

@@ -6,12 +6,12 @@ import numpy as np
 import pytest
 import torch
 
-from util import pkg, oracle, host_triple, seeded_bf16, to_dev_bf16, ref_kernels, REL_TOL, ABS_TOL
+from util import pkg, oracle, host_triple, seeded_bf16, to_dev_bf16, ref_kernels, zipf_bias, exact_prefill, REL_TOL, ABS_TOL
 
 pytestmark = pytest.mark.gpu
 
 
-def build_layer(H, I, E, topk, seed, shared=True, on_gpu=False, router_std=0.02, bias_std=0.1):
+def build_layer(H, I, E, topk, seed, shared=True, on_gpu=False, router_std=0.02, bias_std=0.1, zipf=False):
     """Returns (device layer, host description for the oracle).  on_gpu: weights are drawn and
     quantised on the device (the quantiser is proven bit-exact separately) and only the experts
     a test needs are copied back."""
@@ -19,6 +19,8 @@ def build_layer(H, I, E, topk, seed, shared=True, on_gpu=False, router_std=0.02,
     rng = np.random.default_rng(seed)
     rb = O.f32_to_bf16_bits(rng.normal(0, router_std, (E, H)).astype(np.float32))
     bias = rng.normal(0, bias_std, E).astype(np.float32)
+    if zipf:
+        bias = (bias + zipf_bias(E)).astype(np.float32)
     n = E + (1 if shared else 0)
     dev = []
     if on_gpu:
@@ -175,6 +177,7 @@ def test_moe_prepared_layer_groups_rows_by_expert_beyond_8_tokens(H, I, E, M, to
     xd = torch.from_numpy(x).cuda()
     y_cc, sel_cc, _ = P.moe_forward(layer, xd)
     assert P.moe_prepare(layer)
+    P.set_option(P.OPT_PREFILL_FP4, 0)               # 16 tokens and more would otherwise take the wide GEMM
     try:
         y, sel, wts = check_layer(layer, d, x)
         assert torch.equal(sel, sel_cc)
@@ -185,6 +188,47 @@ def test_moe_prepared_layer_groups_rows_by_expert_beyond_8_tokens(H, I, E, M, to
             assert torch.equal(y1[0], y[m]), m
         assert torch.equal(P.moe_experts(layer, xd, sel, wts), y)
         assert torch.equal(P.moe_forward(layer, xd)[0], y)
+        assert P.device_status() == 0
+    finally:
+        P.set_option(P.OPT_PREFILL_FP4, 1)
+        P.moe_release(layer)
+
+
+@pytest.mark.parametrize('H,I,E,M,topk,shared,zipf', [(1024, 512, 144, 32, 8, True, True), (1024, 512, 144, 128, 8, True, True),
+                                                       (1024, 512, 32, 75, 1, False, False), (1024, 512, 16, 300, 2, True, True),
+                                                       (4096, 1536, 144, 40, 8, True, True)])
+def test_moe_prefill_widths_run_the_grouped_wide_gemm(H, I, E, M, topk, shared, zipf):
+    """16 tokens and more on a prepared layer: pairs sorted by expert on the device, every expert one job per
+    chunk of rows of the wide GEMM (both operands NVFP4), under Zipf(1.1)-skewed routing.  Routing
+    identical to the oracle; output within 1e-3 of the oracle that quantises the activations the same
+    way, a few per cent from the exact block; a token's result independent of its batch; run to run equal."""
+    P, O = pkg(), oracle()
+    layer, d = build_layer(H, I, E, topk, seed=200 + M, shared=shared, on_gpu=H > 1024, zipf=zipf)
+    x = np.random.default_rng(M + I).normal(0, 1, (M, H)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    assert P.moe_prepare(layer)
+    try:
+        y, sel, wts = P.moe_forward(layer, xd)
+        sel_o, wts_o, gap = O.route(O.router_logits(x, d['rb']), d['bias'], topk)
+        assert gap.min() > 1e-6
+        assert np.array_equal(sel.cpu().numpy(), sel_o) and np.abs(wts.cpu().numpy() - wts_o).max() < 1e-5
+        rows = list(range(M)) if H <= 1024 else [0, 1, M // 2, M - 1]         # full geometry: oracle on a few tokens' experts
+        ex = host_experts(d, set(sel_o[rows].ravel().tolist()))
+        sh = ex[E] if shared else None
+        yo = O.moe_experts_act_nvfp4(x[rows], sel_o[rows], wts_o[rows], ex[:E], sh)
+        yh = y.cpu().numpy()[rows]
+        r, a = O.rel_l2(yh, yo), O.max_abs(yh, yo)
+        assert r <= REL_TOL and a <= ABS_TOL, (r, a)
+        exact = O.moe_experts(x[rows], sel_o[rows], wts_o[rows], ex[:E], sh)
+        assert 0.02 < O.rel_l2(yh, exact) < 0.25
+        with exact_prefill():
+            y_exact, _, _ = P.moe_forward(layer, xd)
+        assert O.rel_l2(y_exact.cpu().numpy()[rows], exact) <= REL_TOL
+        assert torch.equal(P.moe_forward(layer, xd)[0], y)
+        assert torch.equal(P.moe_experts(layer, xd, sel, wts), y)
+        lo = M - 16
+        y_sub, _, _ = P.moe_forward(layer, xd[lo:].contiguous())              # the last 16 tokens on their own
+        assert O.rel_l2(y_sub.cpu().numpy(), y.cpu().numpy()[lo:]) < 1e-6
         assert P.device_status() == 0
     finally:
         P.moe_release(layer)
@@ -244,3 +288,33 @@ def test_route_ties_lowest_index_wins():
     assert np.array_equal(sel.cpu().numpy(), so)
     assert list(sel[0, :3].tolist()) == [2, 17, 33]
     assert np.abs(wts.cpu().numpy() - wo).max() < 1e-5
+
+
+def test_moe_expert_tensors_at_the_4_byte_floor():
+    """The reference's checkpoint only guarantees 4-byte aligned packed tensors and scales at any address
+    (kernels/moe.cu:167-174).  The CUDA-core experts must run from there and match the oracle; prepare
+    (the tensor-core experts) declines such a layer instead of faulting."""
+    P, O = pkg(), oracle()
+    H, I, E, topk = 512, 256, 8, 2
+    rng = np.random.default_rng(17)
+    host = [(host_triple((I, H), 9000 + 3 * e), host_triple((I, H), 9001 + 3 * e), host_triple((H, I), 9002 + 3 * e)) for e in range(E + 1)]
+    keep = []
+
+    def shifted(t):
+        p, s, gs = t
+        pb = torch.zeros(p.size + 16, dtype=torch.uint8, device='cuda'); pb[4:4 + p.size] = torch.from_numpy(p).cuda().reshape(-1)
+        sb = torch.zeros(s.size + 16, dtype=torch.uint8, device='cuda'); sb[1:1 + s.size] = torch.from_numpy(s).cuda().reshape(-1)
+        keep.extend([pb, sb])
+        return P.Nvfp4Weight(pb[4:4 + p.size].view(p.shape), sb[1:1 + s.size].view(s.shape), torch.from_numpy(gs).cuda())
+    dev = [tuple(shifted(w) for w in t) for t in host]
+    assert dev[0][0].packed.data_ptr() % 16 == 4 and dev[0][0].scale.data_ptr() % 2 == 1
+    rb = O.f32_to_bf16_bits(rng.normal(0, 0.05, (E, H)).astype(np.float32))
+    bias = rng.normal(0, 0.1, E).astype(np.float32)
+    layer = P.MoeLayer(to_dev_bf16(rb), torch.from_numpy(bias).cuda(), dev[:E], dev[E], topk, H, I)
+    d = dict(rb=rb, bias=bias, host=host, dev=dev, E=E, topk=topk, shared=True)
+    x = rng.normal(0, 1, (3, H)).astype(np.float32)
+    check_layer(layer, d, x)
+    assert P.moe_prepare(layer) is False
+    y, _, _ = P.moe_forward_static(layer, torch.from_numpy(x).cuda())
+    assert torch.isfinite(y).all()
+    assert P.device_status() == 0

@@ -433,3 +433,80 @@ def test_gemv_vs_reference_kernel():
 
 def y_ptr(t):
     return C.c_void_p(t.data_ptr())
+
+
+# ---- dense-layer MLP and the linear-attention sibling groups at their real shapes -------------------
+
+@pytest.mark.parametrize('M,H,I', [(1, 1024, 3072), (3, 512, 768), (1, 4096, 12288)])
+def test_dense_mlp_vs_oracle(M, H, I):
+    """gate/up as one fused launch, clamped SwiGLU, down (reference kernels/layer.cu:235-254)."""
+    P, O = pkg(), oracle()
+    big = H == 4096
+    if big:
+        Ws = [P.quantize(to_dev_bf16(seeded_bf16(sh, 500 + i))) for i, sh in enumerate([(I, H), (I, H), (H, I)])]
+        ts = [W.numpy() for W in Ws]
+    else:
+        ts = [host_triple((I, H), 31), host_triple((I, H), 32), host_triple((H, I), 33)]
+        Ws = [dev_weight(t) for t in ts]
+    x = (np.random.default_rng(M).normal(0, 1, (M, H)) * 30).astype(np.float32)      # large enough to reach the clamps
+    y = P.dense_mlp(torch.from_numpy(x).cuda(), *Ws, limit=10.0).cpu().numpy()
+    ref, act = O.expert_mlp(x, *ts, limit=10.0)
+    assert np.abs(act).max() > 50                     # the clamps are active
+    r = O.rel_l2(y, ref)
+    assert r <= REL_TOL, r
+    assert P.device_status() == 0
+
+
+@pytest.mark.parametrize('Ns,K,own_x', [([8192, 8192, 8192], 4096, False), ([128, 128, 64], 4096, False), ([8192, 8192], 128, True)])
+def test_kda_sibling_groups_real_shapes(Ns, K, own_x):
+    """The fused groups of the linear-attention layer (reference kernels/kda.cu:235-266,
+    tests/gate_gemv_multi.cu:54-61): fused == separate bit for bit, and within tolerance of the oracle."""
+    P, O = pkg(), oracle()
+    Ws = [P.quantize(to_dev_bf16(seeded_bf16((n, K), 600 + i))) for i, n in enumerate(Ns)]
+    rng = np.random.default_rng(K)
+    xh = [rng.normal(0, 1, (1, K)).astype(np.float32) for _ in Ns] if own_x else [rng.normal(0, 1, (1, K)).astype(np.float32)] * len(Ns)
+    xs = [torch.from_numpy(a).cuda() for a in xh]
+    ys = P.gemv_multi(Ws, xs, 1)
+    for W, x, xa, y in zip(Ws, xs, xh, ys):
+        assert torch.equal(P.gemm(W, x), y)
+        rows = slice(0, 512)                              # oracle on the first rows keeps the CPU side short
+        p, s, gs = W.numpy()
+        close(y.cpu().numpy()[:, rows], O.gemm(xa, p[rows], s[rows], gs))
+    assert P.device_status() == 0
+
+
+# ---- robustness ------------------------------------------------------------------------------------
+
+def test_bounded_wait_runs_out_and_reports():
+    """A kernel whose wait can never be satisfied gives up after its limit, the kernel returns, the status
+    word names the site, and the context stays usable (no trap, no hang)."""
+    P = pkg()
+    P.device_status(clear=True)
+    assert P.device_status() == 0
+    P.check(P.lib().b200_nvfp4_selftest_bounded_wait(None), 'selftest')
+    torch.cuda.synchronize()
+    st = P.device_status(clear=True)
+    assert st >> 16 == 15 and (st & 0xffff) == 0, hex(st)
+    assert P.device_status() == 0
+    W = dev_weight(host_triple((64, 256), 3))            # the context still works
+    x = torch.randn(1, 256, device='cuda')
+    assert torch.isfinite(P.gemm(W, x)).all()
+
+
+@pytest.mark.parametrize('umma', ['1', '0'])
+def test_non_finite_activations_propagate(monkeypatch, umma):
+    """A NaN or an infinity in an activation row must not vanish: every output of that row is non-finite on
+    the tensor-core path and on the CUDA-core path alike; other rows are untouched."""
+    monkeypatch.setenv('B200_NVFP4_UMMA', umma)
+    P, O = pkg(), oracle()
+    t = host_triple((300, 1024), 9)
+    W = dev_weight(t)
+    x = np.random.default_rng(2).normal(0, 1, (3, 1024)).astype(np.float32)
+    x[0, 17] = np.nan; x[1, 900] = np.inf
+    y = P.gemm(W, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert not np.isfinite(y[0]).any() and not np.isfinite(y[1]).any()
+    assert O.rel_l2(y[2], O.gemm(x[2:3], *t)[0]) <= REL_TOL
+    # the wide GEMM as well
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    yw = P.gemm_bf16(W, xb).cpu().numpy()
+    assert not np.isfinite(yw[0]).any() and not np.isfinite(yw[1]).any() and np.isfinite(yw[2]).all()

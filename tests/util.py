@@ -64,3 +64,22 @@ def ref_kernels():
     for f in ('ref_moe_hidden', 'ref_moe_inter', 'ref_moe_experts', 'ref_moe_topk'):
         getattr(L, f).restype = ci
     return L
+
+
+def zipf_bias(E, s=1.1, seed=4, strength=0.08):
+    """Expert popularity ~ Zipf(s) over a seeded permutation, as a router ranking bias (the same
+    construction as the benchmark's skewed-routing configurations)."""
+    rng = np.random.default_rng(seed)
+    p = 1.0 / np.arange(1, E + 1) ** s
+    p = p[rng.permutation(E)]
+    return (strength * np.log(p / p.mean())).astype(np.float32)
+
+
+class exact_prefill:
+    """Context: calls with 16 or more rows keep fp32-activation accuracy (B200_OPT_PREFILL_FP4 = 0)."""
+
+    def __enter__(self):
+        pkg().set_option(pkg().OPT_PREFILL_FP4, 0)
+
+    def __exit__(self, *a):
+        pkg().set_option(pkg().OPT_PREFILL_FP4, 1)
