@@ -48,7 +48,9 @@ struct GxParams {
     const unsigned char* sfb;                      // activation scales [K/256][sfb_rows][16]
     size_t sfb_rows;
     unsigned int* status;
-    int n_jobs, K, R, stages, prefetch_before_wait;
+    int n_jobs, K, R, prefetch_before_wait;
+    int sa, sb;                                    // slots of the weight ring (deep: HBM latency) and of the activation / scale ring (L2 latency)
+    uint32_t a_slot;                               // bytes of a weight slot: R x 128 rounded up to 1 KB (the MMA reads 16 KB from its start)
     int sc_box, sc_swz;
     int T;                                         // consecutive weight-row tiles per CTA (T * NT <= 256 accumulator columns, T * K/256 <= 64 steps)
     int sps, nslot;                                // steps per scale slab; slots of the slab ring
@@ -107,7 +109,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
     constexpr int CB = NT / 32;                    // TMEM columns the activation scales of one 64-k block fill
     constexpr int CBS = CB < 4 ? 4 : CB;           // ... and the columns between two blocks (scale addresses stay multiples of 4)
     constexpr int SLOT = 16 + 4 * CBS;             // TMEM columns of one step's scales
-    constexpr uint32_t AB_BYTES = GX_A_BYTES + NT * 128u;
+    constexpr uint32_t B_BYTES = NT * 128u;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t full_bar[GX_MAX_STEPS], sf_bar[GX_MAX_STEPS], empty_bar[GX_MAX_STEPS], slab_bar[GX_MAX_SLABS], done_bar;
     __shared__ uint32_t tmem_base_s;
@@ -138,9 +140,10 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
     const int sps = p.sps;                         // steps one scale slab covers; slab j = steps [j * sps, (j + 1) * sps)
     const uint32_t slab_bytes = (uint32_t)R * (uint32_t)p.sc_box;
 
-    unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
-    unsigned char* scl = ring + (size_t)p.stages * AB_BYTES;                    // ring of weight-scale slabs [R x sc_box], 1 KB aligned (swizzle)
-    unsigned char* sfbs = scl + (size_t)p.nslot * slab_bytes;                   // per stage NT x 16 B of activation scales
+    unsigned char* ringA = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);  // sa slots of packed weights
+    unsigned char* ringB = ringA + (size_t)p.sa * p.a_slot;                     // sb slots of packed activations
+    unsigned char* scl = ringB + (size_t)p.sb * B_BYTES;                        // ring of weight-scale slabs [R x sc_box], 1 KB aligned (swizzle)
+    unsigned char* sfbs = scl + (size_t)p.nslot * slab_bytes;                   // per activation slot NT x 16 B of activation scales
 
     pdl_launch_dependents();
     if (warp >= 4) {
@@ -182,45 +185,49 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
                 mbar_expect_tx(slab0 + j * 8, slab_bytes);
                 gx_tma_2d(smem_u32(scl) + (uint32_t)(j % p.nslot) * slab_bytes, ms, (it / sps) * p.sc_box, rown0, slab0 + j * 8);
             }
-            const int s = g % p.stages;
-            if (g >= p.stages) mbar_wait_spin(empty0 + (g - p.stages) * 8, 0, p.status, 9);
-            const uint32_t bar = full0 + g * 8, dst = smem_u32(ring) + (uint32_t)s * AB_BYTES;
+            // The weights stream from HBM and get the deep ring; the activations come from L2 and share a
+            // short ring with the step's scale slot in TMEM.  Both loads of a step signal one barrier.
+            const int sA = g % p.sa, sB = g % p.sb;
+            if (g >= p.sa) mbar_wait_spin(empty0 + (g - p.sa) * 8, 0, p.status, 9);
+            const uint32_t bar = full0 + g * 8;
             mbar_expect_tx(bar, step_bytes);
-            gx_tma_2d(dst, mw, it * 128, rown0, bar);                             // weights may be read early (stable weights)
+            gx_tma_2d(smem_u32(ringA) + (uint32_t)sA * p.a_slot, mw, it * 128, rown0, bar);     // weights may be read early (stable weights)
             pdl_wait();                                                           // the activations come from the quantiser launch
-            gx_tma_2d(dst + GX_A_BYTES, &map_x, it * 128, J.row0, bar);
-            bulk_g2s(smem_u32(sfbs) + (uint32_t)s * NT * 16u, p.sfb + ((size_t)it * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
+            if (g >= p.sb) mbar_wait_spin(empty0 + (g - p.sb) * 8, 0, p.status, 7);
+            gx_tma_2d(smem_u32(ringB) + (uint32_t)sB * B_BYTES, &map_x, it * 128, J.row0, bar);
+            bulk_g2s(smem_u32(sfbs) + (uint32_t)sB * NT * 16u, p.sfb + ((size_t)it * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
             it += 32; while (it >= nst) { it -= nst; ++t; }
         }
         __syncwarp();
         // The tcgen05.commit arrivals on empty_bar are asynchronous: wait for the last one of every
         // stage, or the CTA could exit with an arrival in flight that lands in the next CTA's shared memory.
-        for (int g = max(0, nsteps - p.stages) + lane; g < nsteps; g += 32)
+        for (int g = max(0, nsteps - p.sa) + lane; g < nsteps; g += 32)
             mbar_wait_spin(empty0 + g * 8, 0, p.status, 10);
         __syncwarp();
     } else if (warp == 1) {
         // ---- MMA issuer: the whole warp walks the loop, lane 0 issues ----
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
-        const uint64_t dA0 = gx_desc(smem_u32(ring)), dB0 = gx_desc(smem_u32(ring) + GX_A_BYTES);
+        const uint64_t dA0 = gx_desc(smem_u32(ringA)), dB0 = gx_desc(smem_u32(ringB));
         const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-        int s = 0, t = 0, it = 0;
+        int sA = 0, sB = 0, t = 0, it = 0;
         for (int g = 0; g < nsteps; ++g) {
             mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
             gx_fence_after();
             if (lane == 0) {
-                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)s * SLOT;
-                const uint64_t so = (uint64_t)(((uint32_t)s * AB_BYTES) >> 4);
+                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)sB * SLOT;
+                const uint64_t soA = (uint64_t)(((uint32_t)sA * p.a_slot) >> 4), soB = (uint64_t)(((uint32_t)sB * B_BYTES) >> 4);
                 #pragma unroll
                 for (int kb = 0; kb < 4; ++kb) {
                     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                                  " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
-                                 :: "r"(tmem + (uint32_t)(t * NT)), "l"(dA0 + so + kb * 2), "l"(dB0 + so + kb * 2), "r"(idesc),
+                                 :: "r"(tmem + (uint32_t)(t * NT)), "l"(dA0 + soA + kb * 2), "l"(dB0 + soB + kb * 2), "r"(idesc),
                                     "r"((uint32_t)((it | kb) != 0)), "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
                 }
                 gx_commit(empty0 + g * 8);
             }
             __syncwarp();
-            if (++s == p.stages) s = 0;
+            if (++sA == p.sa) sA = 0;
+            if (++sB == p.sb) sB = 0;
             if (++it == nst) { it = 0; ++t; }
         }
         if (lane == 0) gx_commit(smem_u32(&done_bar));
@@ -233,7 +240,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         if (tm < NT) sx[tm] = tm < J.rows ? 1.0f / (J.gs_w[0] * J.gs_x[tm]) : 0.f;
         named_sync(1, GX_MOVERS);
         const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]), slab0 = smem_u32(&slab_bar[0]);
-        int s = grp % p.stages;
+        int s = grp % p.sb;
         int t = grp / nst, it = grp - t * nst;
         for (int g = grp; g < nsteps; g += 2) {
             const int j = g / sps, valid = J.N - (tile0 + t) * R;    // weight rows of this tile that exist (may exceed R)
@@ -267,7 +274,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             gx_fence_before();
             mbar_arrive(sf0 + g * 8);
-            s += 2; while (s >= p.stages) s -= p.stages;
+            s += 2; while (s >= p.sb) s -= p.sb;
             it += 2; while (it >= nst) { it -= nst; ++t; }
         }
         // epilogue: group grp takes columns [grp * NT/2, (grp + 1) * NT/2) of every tile
@@ -435,15 +442,17 @@ static int gx_launch_t(GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw
     const int slabs = p.T * (nst / p.sps);
     if (p.T < 1 || p.T * NT > GX_COL_SF || p.T * nst > GX_MAX_STEPS || slabs > GX_MAX_SLABS) return B200_ENOTIMPL;
     p.nslot = std::min(slabs, 3);
-    const size_t fixed = (size_t)p.nslot * p.R * p.sc_box;
-    const size_t per_stage = GX_A_BYTES + (size_t)NT * 128 + (size_t)NT * 16;
-    if (fixed + 2 * per_stage > room) return B200_ENOTIMPL;
-    int stages = (int)std::min<size_t>((room - fixed) / per_stage, (size_t)GX_MAX_STAGES);
-    stages = std::min(stages, (GX_TMEM_COLS - GX_COL_SF) / (16 + 4 * std::max(NT / 32, 4)));
-    stages = std::min(stages, p.T * nst);
-    if (stages < 2 && stages < p.T * nst) return B200_ENOTIMPL;
-    p.stages = stages;
-    const size_t smem = (size_t)stages * per_stage + fixed + 1024;
+    const int nsteps = p.T * nst;
+    p.a_slot = ((uint32_t)p.R * 128u + 1023u) & ~1023u;
+    p.sb = std::min(nsteps, NT >= 256 ? 3 : 4);
+    const size_t fixed = (size_t)p.nslot * p.R * p.sc_box + (size_t)p.sb * ((size_t)NT * 128 + (size_t)NT * 16);
+    if (fixed + 2 * (size_t)p.a_slot + GX_A_BYTES > room) return B200_ENOTIMPL;
+    p.sa = (int)std::min<size_t>((room - fixed - GX_A_BYTES) / p.a_slot + 1, (size_t)std::min(nsteps, 16));
+    if (p.sa < p.sb) p.sb = p.sa;
+    if (p.sa < 2 && p.sa < nsteps) return B200_ENOTIMPL;
+    // the MMA reads 16 KB from the start of a weight slot whatever R: keep that inside the allocation for the last slot
+    size_t smem = (size_t)p.sa * p.a_slot + fixed + 1024;
+    if (smem < (size_t)(p.sa - 1) * p.a_slot + GX_A_BYTES + 1024) smem = (size_t)(p.sa - 1) * p.a_slot + GX_A_BYTES + 1024;
     if (!ready[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ac[0] - static_smem)) != cudaSuccess)
             return launch_failed("gemm_mxf4: cudaFuncSetAttribute");

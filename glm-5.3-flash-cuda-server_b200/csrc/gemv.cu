@@ -211,6 +211,71 @@ k_gemm_dense_row(float* __restrict__ y, const __nv_bfloat16* __restrict__ W, con
     }
 }
 
+// The same product for MANY activation rows in one launch (the router logits of a prefill chunk): a CTA
+// takes ET weight rows x up to 8 activation rows.  Every (weight row, activation row) pair is computed
+// exactly as k_gemm_dense_row computes it -- same split of K over the threads, same FMA order, same
+// reduction order -- so a token's logits, and with them its expert selection, do not depend on how many
+// tokens were routed together.  Each thread keeps its slice of the 8 activation rows in registers and
+// reuses it for the ET weight rows.
+template <int ET>
+__global__ void __launch_bounds__(GEMV_THREADS)
+k_gemm_dense_rows(float* __restrict__ y, const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, int M, int N, int K) {
+    constexpr int TM = 8;
+    __shared__ float part[GEMV_WARPS][ET][TM];
+    const int n0 = blockIdx.x * ET, m0 = blockIdx.y * TM, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int mv = min(TM, M - m0);
+    float acc[ET][TM];
+    #pragma unroll
+    for (int e = 0; e < ET; ++e)
+        #pragma unroll
+        for (int m = 0; m < TM; ++m) acc[e][m] = 0.f;
+    for (int i = threadIdx.x; i < (K >> 3); i += GEMV_THREADS) {
+        float xr[TM][8];
+        #pragma unroll
+        for (int m = 0; m < TM; ++m) {
+            if (m < mv) {
+                const float4* xp = reinterpret_cast<const float4*>(x + (size_t)(m0 + m) * K + (size_t)i * 8);
+                const float4 a = xp[0], b = xp[1];
+                xr[m][0] = a.x; xr[m][1] = a.y; xr[m][2] = a.z; xr[m][3] = a.w; xr[m][4] = b.x; xr[m][5] = b.y; xr[m][6] = b.z; xr[m][7] = b.w;
+            } else {
+                #pragma unroll
+                for (int j = 0; j < 8; ++j) xr[m][j] = 0.f;
+            }
+        }
+        #pragma unroll
+        for (int e = 0; e < ET; ++e) {
+            if (n0 + e >= N) break;
+            const uint4 raw = reinterpret_cast<const uint4*>(W + (size_t)(n0 + e) * K)[i];
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float wf[8];
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
+            #pragma unroll
+            for (int m = 0; m < TM; ++m) {
+                #pragma unroll
+                for (int j = 0; j < 8; ++j) acc[e][m] = fmaf(wf[j], xr[m][j], acc[e][m]);
+            }
+        }
+    }
+    #pragma unroll
+    for (int e = 0; e < ET; ++e)
+        #pragma unroll
+        for (int m = 0; m < TM; ++m) {
+            const float v = warp_sum(acc[e][m]);
+            if (lane == 0) part[warp][e][m] = v;
+        }
+    __syncthreads();
+    if (threadIdx.x < ET * TM) {
+        const int e = threadIdx.x / TM, m = threadIdx.x - e * TM;
+        if (n0 + e < N && m < mv) {
+            float v = 0.f;
+            #pragma unroll
+            for (int w = 0; w < GEMV_WARPS; ++w) v += part[w][e][m];
+            y[(size_t)(m0 + m) * N + n0 + e] = v;
+        }
+    }
+}
+
 __global__ void k_f32_to_bf16(__nv_bfloat16* d, const float* s, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) d[i] = __float2bfloat16(s[i]);
@@ -366,6 +431,12 @@ static int launch_dense(float* y, const void* W, const float* x, int N, int K, i
 int dense_gemm(float* y, const void* W, const float* x, int M, int N, int K, int dtype, cudaStream_t s) {
     if (!y || !W || !x || M < 1 || N < 1 || K < 1) return B200_EINVAL;
     if (dtype != B200_F32 && dtype != B200_BF16) return B200_EINVAL;
+    if (M > 8 && dtype == B200_BF16 && N <= 2048 && K >= 2048 && !(K & 7) && !((uintptr_t)W & 15) && !((uintptr_t)x & 15)) {
+        // many rows against a small bf16 matrix (router logits of a prefill chunk): one launch, same bits per row
+        constexpr int ET = 4;
+        k_gemm_dense_rows<ET><<<dim3((N + ET - 1) / ET, (M + 7) / 8), GEMV_THREADS, 0, s>>>(y, static_cast<const __nv_bfloat16*>(W), x, M, N, K);
+        return check_launch("k_gemm_dense_rows");
+    }
     for (int done = 0; done < M;) {
         const int c = std::min(M - done, 8);
         float* yc = y + (size_t)done * N;

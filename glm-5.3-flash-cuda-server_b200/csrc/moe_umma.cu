@@ -31,7 +31,8 @@ constexpr int MU_MAX_TOKENS = 8;
 struct Prepared {
     const b200_nvfp4_mat* experts; const b200_nvfp4_mat* shared;     // key
     int E, H, I;
-    unsigned char* maps;          // device: [(E + 1) experts][3 matrices][w, s] x 128 bytes; shared expert last
+    unsigned char* maps;          // device: [(E + 1) experts][3 matrices][w, s] x 128 bytes, shared expert last; then the same again
+                                  // with boxes 128 rows tall, for the wide GEMM (MU_GX_MAPS bytes further on)
     int R_gu, R_d;
     int device;
 };
@@ -283,7 +284,7 @@ k_moe_group_gx(const __grid_constant__ MoePlan q, const int32_t* __restrict__ se
     }
     for (int e = threadIdx.x; e < G; e += blockDim.x) {
         const b200_nvfp4_mat* mats = e < q.E ? q.experts + (size_t)e * 3 : q.shared;
-        const unsigned char* mp = q.maps + (size_t)e * 6 * 128;
+        const unsigned char* mp = q.maps + (size_t)(q.E + 1) * 6 * 128 + (size_t)e * 6 * 128;     // the 128-row boxes
         for (int c = 0; c * NT < cnt[e]; ++c) {
             const int idx = jstart[e] + c, rows = min(NT, cnt[e] - NT * c), pos0 = off[e] + NT * c;
             j1[2 * idx] = GxJob{q.gbuf + (size_t)pos0 * q.I, mats[0].gscale, gsx1 + pos0, mp, mp + 128, pos0, rows, q.I, q.I};
@@ -341,9 +342,9 @@ static int moe_gx_grouped(const float* x, const b200_moe_layer* L, float* y, con
     if (int rc = quant_act_launch(1, x, nullptr, 0.f, src_row, nullptr, pairs, pairs, H, xq1, sf1, padrows, gs1, s)) return rc;
     // jobs the table is likely to hold: every expert that can be hit once, plus the extra chunks of busy experts
     const long expect = std::min<long>(L->n_expert, (long)M * L->topk) + (L->shared ? 1 : 0) + pairs / NT;
-    if (int rc = gemm_mxf4_table(j1, 2 * max_jobs, 2 * expect, NT, I, H, P->R_gu, xq1, (size_t)pairs, sf1, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = gemm_mxf4_table(j1, 2 * max_jobs, 2 * expect, NT, I, H, 128, xq1, (size_t)pairs, sf1, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
     if (int rc = quant_act_launch(2, q.gbuf, q.ubuf, L->swiglu_limit, nullptr, nullptr, pairs, pairs, I, xq2, sf2, padrows, gs2, s)) return rc;
-    if (int rc = gemm_mxf4_table(j2, max_jobs, expect, NT, H, I, P->R_d, xq2, (size_t)pairs, sf2, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = gemm_mxf4_table(j2, max_jobs, expect, NT, H, I, 128, xq2, (size_t)pairs, sf2, padrows, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
     const int y4 = M * (H >> 2);
     k_moe_combine<<<(y4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, posof, M, q.topk, ns, H);
     return check_launch("k_moe_combine");
@@ -397,13 +398,17 @@ extern "C" int b200_moe_prepare(const b200_moe_layer* L) {
     const int ns = L->topk + (L->shared ? 1 : 0);
     P.R_gu = pick_rows(2 * ns, L->inter);
     P.R_d = pick_rows(ns, L->hidden);
-    std::vector<unsigned char> host((size_t)nexp * 6 * 128);
+    std::vector<unsigned char> host((size_t)nexp * 12 * 128);
     for (int e = 0; e < nexp; ++e) {
         const b200_nvfp4_mat* m = &mats[(size_t)e * 3];
         unsigned char* o = host.data() + (size_t)e * 6 * 128;
         if (umma_encode_maps(o, o + 128, m[0].packed, m[0].scale, L->inter, L->hidden, P.R_gu) ||
             umma_encode_maps(o + 256, o + 384, m[1].packed, m[1].scale, L->inter, L->hidden, P.R_gu) ||
             umma_encode_maps(o + 512, o + 640, m[2].packed, m[2].scale, L->hidden, L->inter, P.R_d)) return B200_ENOTIMPL;
+        o += (size_t)nexp * 6 * 128;                     // the wide GEMM's boxes: always 128 rows
+        if (umma_encode_maps(o, o + 128, m[0].packed, m[0].scale, L->inter, L->hidden, 128) ||
+            umma_encode_maps(o + 256, o + 384, m[1].packed, m[1].scale, L->inter, L->hidden, 128) ||
+            umma_encode_maps(o + 512, o + 640, m[2].packed, m[2].scale, L->hidden, L->inter, 128)) return B200_ENOTIMPL;
     }
     if (cudaGetDevice(&P.device) != cudaSuccess) return launch_failed("moe_prepare: cudaGetDevice");
     if (cudaMalloc(&P.maps, host.size()) != cudaSuccess) return launch_failed("moe_prepare: cudaMalloc");

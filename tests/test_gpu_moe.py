@@ -318,3 +318,17 @@ def test_moe_expert_tensors_at_the_4_byte_floor():
     y, _, _ = P.moe_forward_static(layer, torch.from_numpy(x).cuda())
     assert torch.isfinite(y).all()
     assert P.device_status() == 0
+
+
+def test_router_of_a_batch_equals_router_of_each_token_bitwise():
+    """The one-launch router product for many tokens computes every (token, expert) logit exactly as the
+    single-token call does, so a token's selection does not depend on how many tokens were routed together."""
+    P = pkg()
+    layer, d = build_layer(4096, 256, 144, 8, seed=77)
+    x = torch.randn((45, 4096), device='cuda')
+    sel, wts, logits = P.moe_route(layer, x)
+    for m in (0, 7, 8, 23, 44):
+        s1, w1, l1 = P.moe_route(layer, x[m:m + 1].contiguous())
+        assert torch.equal(l1[0], logits[m]) and torch.equal(s1[0], sel[m]) and torch.equal(w1[0], wts[m]), m
+    s8, w8, l8 = P.moe_route(layer, x[:8].contiguous())
+    assert torch.equal(l8, logits[:8])
