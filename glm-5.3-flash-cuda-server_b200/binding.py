@@ -43,6 +43,10 @@ class EpStats(C.Structure):
                 ('experts_us', C.c_float), ('combine_us', C.c_float), ('total_us', C.c_float), ('pad2', C.c_float)]
 
 
+class OverlayEntry(C.Structure):
+    _fields_ = [('packed', C.c_void_p), ('scale', C.c_void_p), ('gscale', C.c_float), ('N', C.c_int), ('K', C.c_int)]
+
+
 class B200Error(RuntimeError):
     pass
 
@@ -84,6 +88,14 @@ def lib():
         L.b200_ep_forward.argtypes = [vp, vp, vp, vp, vp, ci, vp]
         L.b200_ep_last_stats.argtypes = [vp, C.POINTER(EpStats)]
         L.b200_ep_destroy.argtypes = [vp]
+        L.b200_overlay_writer_open.argtypes = [C.POINTER(vp), C.c_char_p, C.c_uint64]
+        L.b200_overlay_writer_add.argtypes = [vp, C.c_char_p, vp, vp, C.c_float, ci, ci]
+        L.b200_overlay_writer_close.argtypes = [vp]
+        L.b200_overlay_family.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p]
+        L.b200_overlay_open.argtypes = [C.POINTER(vp), C.c_char_p]
+        L.b200_overlay_count.argtypes = [vp]
+        L.b200_overlay_find.argtypes = [vp, C.c_char_p, C.POINTER(OverlayEntry)]
+        L.b200_overlay_close.argtypes = [vp]
         L.b200_moe_prepare.argtypes = [C.POINTER(MoeLayerC)]
         L.b200_moe_release.argtypes = [C.POINTER(MoeLayerC)]
         _lib = L
@@ -95,6 +107,8 @@ EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_statu
            'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_dense_mlp_workspace_bytes', 'b200_dense_mlp', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
            'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release',
+           'b200_overlay_writer_open', 'b200_overlay_writer_add', 'b200_overlay_writer_close', 'b200_overlay_family',
+           'b200_overlay_open', 'b200_overlay_count', 'b200_overlay_find', 'b200_overlay_close',
            'b200_ep_unique_id', 'b200_ep_create', 'b200_ep_forward', 'b200_ep_last_stats', 'b200_ep_destroy']
 
 
@@ -403,3 +417,48 @@ class EpContext:
         if self.h:
             check(lib().b200_ep_destroy(self.h), 'b200_ep_destroy')
             self.h = C.c_void_p(0)
+
+
+class OverlayWriter:
+    """safetensors overlay of NVFP4 triples, byte-compatible with the reference's requant tool."""
+
+    def __init__(self, directory, shard_bytes=0):
+        self.h = C.c_void_p(0)
+        check(lib().b200_overlay_writer_open(C.byref(self.h), directory.encode(), shard_bytes), 'b200_overlay_writer_open')
+
+    def add(self, name, packed, scale, gscale):
+        """packed u8 [N,K/2], scale u8 [N,K/16]: numpy arrays (host); gscale: float."""
+        packed = np.ascontiguousarray(packed, np.uint8); scale = np.ascontiguousarray(scale, np.uint8)
+        N, K = packed.shape[0], packed.shape[1] * 2
+        check(lib().b200_overlay_writer_add(self.h, name.encode(), packed.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p),
+                                            C.c_float(float(gscale)), N, K), 'b200_overlay_writer_add')
+
+    def close(self):
+        check(lib().b200_overlay_writer_close(self.h), 'b200_overlay_writer_close')
+        self.h = C.c_void_p(0)
+
+
+def overlay_family(arch, families, name):
+    return lib().b200_overlay_family(arch.encode(), families.encode() if families else None, name.encode())
+
+
+class Overlay:
+    """Reader: maps an overlay directory; triple(name) -> (packed, scale, gscale) numpy copies."""
+
+    def __init__(self, directory):
+        self.h = C.c_void_p(0)
+        check(lib().b200_overlay_open(C.byref(self.h), directory.encode()), 'b200_overlay_open')
+
+    def __len__(self):
+        return lib().b200_overlay_count(self.h)
+
+    def triple(self, name):
+        e = OverlayEntry()
+        check(lib().b200_overlay_find(self.h, name.encode(), C.byref(e)), 'b200_overlay_find')
+        p = np.ctypeslib.as_array(C.cast(e.packed, C.POINTER(C.c_uint8)), shape=(e.N, e.K // 2)).copy()
+        s = np.ctypeslib.as_array(C.cast(e.scale, C.POINTER(C.c_uint8)), shape=(e.N, e.K // 16)).copy()
+        return p, s, np.array([e.gscale], np.float32), (e.packed % 16 == 0 and e.scale % 16 == 0)
+
+    def close(self):
+        check(lib().b200_overlay_close(self.h), 'b200_overlay_close')
+        self.h = C.c_void_p(0)

@@ -240,6 +240,31 @@ size_t b200_moe_static_ws_limit(void);
 int b200_moe_forward_static(const float* x, const b200_moe_layer* L, float* y, int32_t* sel,
                             float* wts, int M, b200_stream stream);
 
+/* ---- safetensors overlay of NVFP4 triples (host side; no GPU involved) ---------------------------
+ * The wire format of the reference's requant tool (tools/requant_dense_nvfp4.py:123-152 ShardWriter,
+ * :224-239): per selected tensor `<stem>.weight` the three tensors `<stem>.weight_packed` (U8),
+ * `.weight_scale` (F8_E4M3), `.weight_global_scale` (F32) in shards overlay-%05d.safetensors whose data
+ * and every tensor start on 16-byte boundaries, plus model.safetensors.index.json.  The writer emits the
+ * same bytes as that tool for the same tensors in the same order, so an overlay requantised on the GPU
+ * (b200_nvfp4_quantize, copied back) loads through the reference's own loader (include/safetensors.h:54-113,
+ * include/weight_store.h:23-33).  packed / scale are HOST buffers; a new shard starts once the current
+ * one holds shard_bytes (0 = the tool's default, 2 GiB).  close writes the last shard and the index.
+ * b200_overlay_family: index of the first family of `families_csv` (NULL = the arch's default list) whose
+ * pattern matches the tensor name (:76-120, arch "glm5" or "mimo"), -1 = not selected, -2 = unknown name.
+ * The reader maps an overlay directory and hands out host pointers to a triple (valid until close). */
+typedef struct b200_overlay_writer b200_overlay_writer;
+typedef struct b200_overlay b200_overlay;
+typedef struct { const uint8_t* packed; const uint8_t* scale; float gscale; int N; int K; } b200_overlay_entry;
+int b200_overlay_writer_open(b200_overlay_writer** out, const char* dir, uint64_t shard_bytes);
+int b200_overlay_writer_add(b200_overlay_writer* w, const char* tensor_name, const uint8_t* packed,
+                            const uint8_t* scale, float gscale, int N, int K);
+int b200_overlay_writer_close(b200_overlay_writer* w);
+int b200_overlay_family(const char* arch, const char* families_csv, const char* tensor_name);
+int b200_overlay_open(b200_overlay** out, const char* dir);
+int b200_overlay_count(const b200_overlay* o);
+int b200_overlay_find(const b200_overlay* o, const char* tensor_name, b200_overlay_entry* out);
+int b200_overlay_close(b200_overlay* o);
+
 /* ---- expert-parallel MoE layer (one process per GPU, NCCL) ------------------------------------
  * The reference has no multi-GPU form (all experts sit behind one device table, src/engine.cu:168-195);
  * this is the same block (kernels/moe.cu:669-740, fixed-order gate sum :584-597) with the experts of a

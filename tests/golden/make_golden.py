@@ -209,7 +209,48 @@ def case_moe():
     np.savez_compressed(os.path.join(OUT, 'moe.npz'), **out)
 
 
+def case_overlay():
+    """A tiny bf16 'checkpoint' (two safetensors shards; names that hit, miss and are excluded by the family
+    tables; a non-bf16 tensor; a K that is not a multiple of 16) and the overlay the reference's own tool
+    writes for it: tools/requant_dense_nvfp4.py run unmodified as a program."""
+    import json, shutil, struct, subprocess
+    mdir, odir = os.path.join(OUT, 'overlay_model'), os.path.join(OUT, 'overlay')
+    for d in (mdir, odir):
+        shutil.rmtree(d, ignore_errors=True); os.makedirs(d)
+    rng = np.random.default_rng(4242)
+
+    def bf(shape, std=0.02):
+        return to_bf16_bits(rng.normal(0.0, std, shape).astype(np.float32))
+    shards = [
+        [('model.layers.0.self_attn.q_proj.weight', 'BF16', bf((64, 256))),
+         ('model.layers.0.self_attn.o_proj.weight', 'BF16', bf((32, 128))),
+         ('model.layers.0.mlp.gate.weight', 'BF16', bf((8, 64))),
+         ('model.visual.layers.0.self_attn.o_proj.weight', 'BF16', bf((16, 32))),
+         ('model.layers.1.mlp.down_proj.weight', 'BF16', bf((48, 96), 0.05)),
+         ('model.layers.1.self_attn.kv_b_proj.weight', 'BF16', bf((16, 32))),
+         ('model.embed_tokens.weight', 'BF16', bf((20, 32))),
+         ('model.layers.2.mlp.up_proj.weight', 'F32', rng.normal(0, 0.02, (8, 32)).astype(np.float32)),
+         ('model.layers.2.self_attn.f_a_proj.weight', 'BF16', bf((16, 40)))],
+        [('lm_head.weight', 'BF16', bf((100, 64))),
+         ('model.layers.3.self_attn.indexer.wk.weight', 'BF16', bf((24, 32))),
+         ('model.layers.3.self_attn.index_kpool_compress_gate', 'BF16', bf((4, 16), 1.0)),
+         ('model.layers.3.self_attn.g_b_proj.weight', 'BF16', np.zeros((8, 16), np.uint16))],
+    ]
+    for i, tensors in enumerate(shards):
+        meta, blob, off = {}, b'', 0
+        for name, dt, arr in tensors:
+            b = arr.tobytes()
+            meta[name] = {'dtype': dt, 'shape': list(arr.shape), 'data_offsets': [off, off + len(b)]}
+            blob += b; off += len(b)
+        hdr = json.dumps(meta, separators=(',', ':')).encode()
+        with open(os.path.join(mdir, 'model-%05d-of-00002.safetensors' % (i + 1)), 'wb') as f:
+            f.write(struct.pack('<Q', len(hdr))); f.write(hdr); f.write(blob)
+    subprocess.check_call([sys.executable, os.path.join(REF, 'tools', 'requant_dense_nvfp4.py'), '--model', mdir, '--out', odir,
+                           '--rows', '16', '--shard-bytes', '12000'])
+
+
 if __name__ == '__main__':
+    case_overlay()
     case_tables(); case_quant(); case_edges(); case_gemv(); case_gemm_act(); case_moe()
     for f in sorted(os.listdir(OUT)):
         if f.endswith('.npz'):

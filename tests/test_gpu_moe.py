@@ -324,7 +324,7 @@ def test_router_of_a_batch_equals_router_of_each_token_bitwise():
     """The one-launch router product for many tokens computes every (token, expert) logit exactly as the
     single-token call does, so a token's selection does not depend on how many tokens were routed together."""
     P = pkg()
-    layer, d = build_layer(4096, 256, 144, 8, seed=77)
+    layer, d = build_layer(4096, 256, 144, 8, seed=77, on_gpu=True)
     x = torch.randn((45, 4096), device='cuda')
     sel, wts, logits = P.moe_route(layer, x)
     for m in (0, 7, 8, 23, 44):
