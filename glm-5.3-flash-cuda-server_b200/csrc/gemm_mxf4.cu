@@ -30,6 +30,7 @@
 #include "tma_pipe.cuh"
 #include <cuda.h>
 #include <cstdio>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -49,7 +50,7 @@ struct GxParams {
     size_t sfb_rows;
     unsigned int* status;
     int n_jobs, K, R, prefetch_before_wait;
-    int sa, sb;                                    // slots of the weight ring (deep: HBM latency) and of the activation / scale ring (L2 latency)
+    int sa, sb, ssf;                               // slots of the weight ring, of the activation ring, and of the scale slots in TMEM (ssf <= sb)
     uint32_t a_slot;                               // bytes of a weight slot: R x 128 rounded up to 1 KB (the MMA reads 16 KB from its start)
     int sc_box, sc_swz;
     int T;                                         // consecutive weight-row tiles per CTA (T * NT <= 256 accumulator columns, T * K/256 <= 64 steps)
@@ -209,12 +210,12 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
         const uint64_t dA0 = gx_desc(smem_u32(ringA)), dB0 = gx_desc(smem_u32(ringB));
         const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
-        int sA = 0, sB = 0, t = 0, it = 0;
+        int sA = 0, sB = 0, sF = 0, t = 0, it = 0;
         for (int g = 0; g < nsteps; ++g) {
             mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
             gx_fence_after();
             if (lane == 0) {
-                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)sB * SLOT;
+                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)sF * SLOT;
                 const uint64_t soA = (uint64_t)(((uint32_t)sA * p.a_slot) >> 4), soB = (uint64_t)(((uint32_t)sB * B_BYTES) >> 4);
                 #pragma unroll
                 for (int kb = 0; kb < 4; ++kb) {
@@ -228,6 +229,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             __syncwarp();
             if (++sA == p.sa) sA = 0;
             if (++sB == p.sb) sB = 0;
+            if (++sF == p.ssf) sF = 0;
             if (++it == nst) { it = 0; ++t; }
         }
         if (lane == 0) gx_commit(smem_u32(&done_bar));
@@ -240,12 +242,16 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         if (tm < NT) sx[tm] = tm < J.rows ? 1.0f / (J.gs_w[0] * J.gs_x[tm]) : 0.f;
         named_sync(1, GX_MOVERS);
         const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]), slab0 = smem_u32(&slab_bar[0]);
-        int s = grp % p.sb;
+        const uint32_t empty0 = smem_u32(&empty_bar[0]);
+        int s = grp % p.sb, sf = grp % p.ssf;
         int t = grp / nst, it = grp - t * nst;
         for (int g = grp; g < nsteps; g += 2) {
             const int j = g / sps, valid = J.N - (tile0 + t) * R;    // weight rows of this tile that exist (may exceed R)
             mbar_wait_spin(slab0 + j * 8, 0, p.status, 12);
             mbar_wait_spin(full0 + g * 8, 0, p.status, 13);
+            // the scale slot in TMEM is free once the MMAs of the step that used it last have completed
+            // (implied by full[g] when there are as many slots as activation slots)
+            if (p.ssf < p.sb && g >= p.ssf) mbar_wait_spin(empty0 + (g - p.ssf) * 8, 0, p.status, 6);
             // weights: lane l holds rows l, l+32, l+64, l+96, 16 bytes each = four 64-k blocks x four scales;
             // block kb of row 32c + l goes to column kb*4 + c
             const unsigned char* sl = scl + (size_t)(j % p.nslot) * slab_bytes;
@@ -268,13 +274,14 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
                 const uint4 v = c < CB ? *reinterpret_cast<const uint4*>(sb + (size_t)(lane + 32 * c) * 16) : make_uint4(0u, 0u, 0u, 0u);
                 rb[c] = v.x; rb[CBS + c] = v.y; rb[2 * CBS + c] = v.z; rb[3 * CBS + c] = v.w;
             }
-            const uint32_t slot = tq + GX_COL_SF + (uint32_t)s * SLOT;
+            const uint32_t slot = tq + GX_COL_SF + (uint32_t)sf * SLOT;
             GxSt<16>::st(slot, ra);
             GxSt<4 * CBS>::st(slot + 16, rb);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             gx_fence_before();
             mbar_arrive(sf0 + g * 8);
             s += 2; while (s >= p.sb) s -= p.sb;
+            sf += 2; while (sf >= p.ssf) sf -= p.ssf;
             it += 2; while (it >= nst) { it -= nst; ++t; }
         }
         // epilogue: group grp takes columns [grp * NT/2, (grp + 1) * NT/2) of every tile
@@ -444,12 +451,28 @@ static int gx_launch_t(GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw
     p.nslot = std::min(slabs, 3);
     const int nsteps = p.T * nst;
     p.a_slot = ((uint32_t)p.R * 128u + 1023u) & ~1023u;
-    p.sb = std::min(nsteps, NT >= 256 ? 3 : 4);
-    const size_t fixed = (size_t)p.nslot * p.R * p.sc_box + (size_t)p.sb * ((size_t)NT * 128 + (size_t)NT * 16);
-    if (fixed + 2 * (size_t)p.a_slot + GX_A_BYTES > room) return B200_ENOTIMPL;
-    p.sa = (int)std::min<size_t>((room - fixed - GX_A_BYTES) / p.a_slot + 1, (size_t)std::min(nsteps, 16));
-    if (p.sa < p.sb) p.sb = p.sa;
-    if (p.sa < 2 && p.sa < nsteps) return B200_ENOTIMPL;
+    // Ring depths: a step is in flight from the moment its loads are issued until its MMAs complete, and both
+    // the weights (HBM) and the activations (L2, but requested by every CTA at once) take a microsecond or
+    // more to arrive, so the shallower of the two rings bounds the step rate.  Take the split of the shared
+    // memory that makes the shallower ring as deep as possible (ties: the deeper weight ring).
+    const size_t b_slot = (size_t)NT * 128 + (size_t)NT * 16, slab_sz = (size_t)p.nslot * p.R * p.sc_box;
+    p.sa = 0; p.sb = 0;
+    for (int sb = std::min(nsteps, 16); sb >= 1; --sb) {
+        const size_t fx = slab_sz + (size_t)sb * b_slot;
+        if (fx + (size_t)p.a_slot + GX_A_BYTES > room) continue;
+        const int sa = (int)std::min<size_t>((room - fx - GX_A_BYTES) / p.a_slot + 1, (size_t)std::min(nsteps, 16));
+        if (std::min(sa, sb) > std::min(p.sa, p.sb) || (std::min(sa, sb) == std::min(p.sa, p.sb) && sa > p.sa)) { p.sa = sa; p.sb = sb; }
+    }
+    if (const char* e = getenv("B200_GX_RINGS")) {       // tuning aid: "sa,sb" replaces the choice above when it fits
+        int ua = 0, ub = 0;
+        if (sscanf(e, "%d,%d", &ua, &ub) == 2 && ua >= 1 && ub >= 1 && ub <= 16 && ua <= 16) {
+            ua = std::min(ua, nsteps); ub = std::min(ub, nsteps);
+            if (slab_sz + (size_t)ub * b_slot + (size_t)(ua - 1) * p.a_slot + GX_A_BYTES <= room) { p.sa = ua; p.sb = ub; }
+        }
+    }
+    if (p.sa < 1 || (std::min(p.sa, p.sb) < 2 && nsteps > 1)) return B200_ENOTIMPL;
+    p.ssf = std::min(p.sb, (GX_TMEM_COLS - GX_COL_SF) / (16 + 4 * std::max(NT / 32, 4)));
+    const size_t fixed = slab_sz + (size_t)p.sb * b_slot;
     // the MMA reads 16 KB from the start of a weight slot whatever R: keep that inside the allocation for the last slot
     size_t smem = (size_t)p.sa * p.a_slot + fixed + 1024;
     if (smem < (size_t)(p.sa - 1) * p.a_slot + GX_A_BYTES + 1024) smem = (size_t)(p.sa - 1) * p.a_slot + GX_A_BYTES + 1024;
