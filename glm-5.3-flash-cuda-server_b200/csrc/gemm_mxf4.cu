@@ -55,6 +55,7 @@ struct GxParams {
     int sc_box, sc_swz;
     int T;                                         // consecutive weight-row tiles per CTA (T * NT <= 256 accumulator columns, T * K/256 <= 64 steps)
     int sps, nslot;                                // steps per scale slab; slots of the slab ring
+    int nacc;                                      // accumulators per tile (1, 2 or 4): k-block it adds into accumulator it % nacc
 };
 
 __device__ __forceinline__ void gx_tma_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
@@ -153,7 +154,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         else if (i >= 64 && i < 64 + nsteps) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
         else if (i >= 128 && i < 128 + nsteps) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
         else if (i >= 192 && i < 192 + GX_MAX_SLABS) mbar_init(smem_u32(&slab_bar[i - 192]), 1);
-        else if (i == 255) mbar_init(smem_u32(&done_bar), 1);
+        else if (i == 255) mbar_init(smem_u32(&done_bar), p.nacc >= 2 ? 2 : 1);
         mbar_fence_init();
     }
     if (warp == 2) {
@@ -176,15 +177,17 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), slab0 = smem_u32(&slab_bar[0]);
         const uint32_t step_bytes = (uint32_t)R * 128u + NT * 128u + NT * 16u;
         int t = lane / nst, it = lane - t * nst;
+        const int spt = nst / sps;                 // slabs per tile
         for (int g = lane; g < nsteps; g += 32) {
             const int rown0 = (tile0 + t) * R;
-            if (it % sps == 0) {
+            const int js = p.sc_swz ? (it >> 3) : 0;                 // slab of this step within its tile
+            if ((p.sc_swz ? (it & 7) : it) == 0) {
                 // the slab of scale rows that steps [g, g + sps) read; its slot is free once the MMAs of the
                 // last step of the slab that held it have completed (their scale movers are then done as well)
-                const int j = g / sps;
+                const int j = t * spt + js;
                 if (j >= p.nslot) mbar_wait_spin(empty0 + ((j - p.nslot + 1) * sps - 1) * 8, 0, p.status, 8);
                 mbar_expect_tx(slab0 + j * 8, slab_bytes);
-                gx_tma_2d(smem_u32(scl) + (uint32_t)(j % p.nslot) * slab_bytes, ms, (it / sps) * p.sc_box, rown0, slab0 + j * 8);
+                gx_tma_2d(smem_u32(scl) + (uint32_t)(j % p.nslot) * slab_bytes, ms, js * p.sc_box, rown0, slab0 + j * 8);
             }
             // The weights stream from HBM and get the deep ring; the activations come from L2 and share a
             // short ring with the step's scale slot in TMEM.  Both loads of a step signal one barrier.
@@ -205,28 +208,38 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         for (int g = max(0, nsteps - p.sa) + lane; g < nsteps; g += 32)
             mbar_wait_spin(empty0 + g * 8, 0, p.status, 10);
         __syncwarp();
-    } else if (warp == 1) {
-        // ---- MMA issuer: the whole warp walks the loop, lane 0 issues ----
+    } else if (warp == 1 || (warp == 3 && p.nacc >= 2)) {
+        // ---- MMA issuers: the whole warp walks the loop, lane 0 issues ----
+        // A chain of MMAs into one accumulator runs at the latency of an MMA, not at its issue rate, and
+        // that latency (about 110 cycles) exceeds the execution time of an MMA narrower than 256 columns.
+        // So a tile has nacc accumulators -- k-block `it` adds into accumulator it % nacc, the epilogue adds
+        // them up in a fixed order -- and with two or more of them two warps issue: warp 1 the even
+        // k-blocks, warp 3 the odd ones (different accumulators, so no order between the warps matters).
+        const int mwi = warp == 1 ? 0 : 1, two = p.nacc >= 2;
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
         const uint64_t dA0 = gx_desc(smem_u32(ringA)), dB0 = gx_desc(smem_u32(ringB));
         const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
         int sA = 0, sB = 0, sF = 0, t = 0, it = 0;
         for (int g = 0; g < nsteps; ++g) {
-            mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
-            gx_fence_after();
-            if (lane == 0) {
-                const uint32_t slot = tmem + GX_COL_SF + (uint32_t)sF * SLOT;
-                const uint64_t soA = (uint64_t)(((uint32_t)sA * p.a_slot) >> 4), soB = (uint64_t)(((uint32_t)sB * B_BYTES) >> 4);
-                #pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                                 " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
-                                 :: "r"(tmem + (uint32_t)(t * NT)), "l"(dA0 + soA + kb * 2), "l"(dB0 + soB + kb * 2), "r"(idesc),
-                                    "r"((uint32_t)((it | kb) != 0)), "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
+            if (!two || (it & 1) == mwi) {
+                mbar_wait_spin(sf0 + g * 8, 0, p.status, 11);
+                gx_fence_after();
+                if (lane == 0) {
+                    const uint32_t slot = tmem + GX_COL_SF + (uint32_t)sF * SLOT;
+                    const uint64_t soA = (uint64_t)(((uint32_t)sA * p.a_slot) >> 4), soB = (uint64_t)(((uint32_t)sB * B_BYTES) >> 4);
+                    const uint32_t tD = tmem + (uint32_t)((t * p.nacc + (it & (p.nacc - 1))) * NT);
+                    const uint32_t first = it < p.nacc ? 0u : 1u;           // the first k-block of an accumulator starts it
+                    #pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                     " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+                                     :: "r"(tD), "l"(dA0 + soA + kb * 2), "l"(dB0 + soB + kb * 2), "r"(idesc),
+                                        "r"(kb ? 1u : first), "r"(slot + kb * 4), "r"(slot + 16 + kb * CBS) : "memory");
+                    }
+                    gx_commit(empty0 + g * 8);
                 }
-                gx_commit(empty0 + g * 8);
+                __syncwarp();
             }
-            __syncwarp();
             if (++sA == p.sa) sA = 0;
             if (++sB == p.sb) sB = 0;
             if (++sF == p.ssf) sF = 0;
@@ -245,8 +258,10 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         const uint32_t empty0 = smem_u32(&empty_bar[0]);
         int s = grp % p.sb, sf = grp % p.ssf;
         int t = grp / nst, it = grp - t * nst;
+        const int spt = nst / sps;
         for (int g = grp; g < nsteps; g += 2) {
-            const int j = g / sps, valid = J.N - (tile0 + t) * R;    // weight rows of this tile that exist (may exceed R)
+            const int js = p.sc_swz ? (it >> 3) : 0, is = p.sc_swz ? (it & 7) : it;     // slab within the tile, step within the slab
+            const int j = t * spt + js, valid = J.N - (tile0 + t) * R;    // weight rows of this tile that exist (may exceed R)
             mbar_wait_spin(slab0 + j * 8, 0, p.status, 12);
             mbar_wait_spin(full0 + g * 8, 0, p.status, 13);
             // the scale slot in TMEM is free once the MMAs of the step that used it last have completed
@@ -255,7 +270,6 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             // weights: lane l holds rows l, l+32, l+64, l+96, 16 bytes each = four 64-k blocks x four scales;
             // block kb of row 32c + l goes to column kb*4 + c
             const unsigned char* sl = scl + (size_t)(j % p.nslot) * slab_bytes;
-            const int is = it - (it / sps) * sps;                    // step within its slab
             uint32_t ra[16];
             #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -295,16 +309,23 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             #pragma unroll 1
             for (int c0 = grp * (NT / 2); c0 < (grp + 1) * (NT / 2); c0 += 16) {
                 if (c0 >= J.rows) break;             // warp-uniform: the remaining tokens do not exist
-                uint32_t d[16];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
-                               "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
-                             : "r"(tq + (uint32_t)(te * NT + c0)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float d[16];
+                #pragma unroll 1
+                for (int a = 0; a < p.nacc; ++a) {
+                    uint32_t v[16];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                                 : "r"(tq + (uint32_t)((te * p.nacc + a) * NT + c0)));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    #pragma unroll
+                    for (int j = 0; j < 16; ++j) d[j] = a == 0 ? __uint_as_float(v[j]) : d[j] + __uint_as_float(v[j]);     // accumulators in index order
+                    if (a + 1 < p.nacc && (a + 1) >= nst) break;     // fewer k-blocks than accumulators: the rest were never started
+                }
                 if (ok) {
                     #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c0 + j < J.rows) J.y[(size_t)(c0 + j) * J.ldy + row] = __uint_as_float(d[j]) * sx[c0 + j];
+                        if (c0 + j < J.rows) J.y[(size_t)(c0 + j) * J.ldy + row] = d[j] * sx[c0 + j];
                 }
             }
         }
@@ -395,6 +416,7 @@ k_quant_act(const void* __restrict__ xin, const void* __restrict__ xin2, float l
 }
 
 // ---- host side ---------------------------------------------------------------------------------
+static int gx_accumulators(int NT);
 static size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 size_t gemm_mxf4_ws_bytes(int M, int K) {
@@ -447,7 +469,8 @@ static int gx_launch_t(GxParams& p, const CUtensorMap& mx, const CUtensorMap& mw
     const int nst = p.K / 256;
     p.sps = p.sc_swz ? 8 : nst;
     const int slabs = p.T * (nst / p.sps);
-    if (p.T < 1 || p.T * NT > GX_COL_SF || p.T * nst > GX_MAX_STEPS || slabs > GX_MAX_SLABS) return B200_ENOTIMPL;
+    p.nacc = gx_accumulators(NT);
+    if (p.T < 1 || p.T * p.nacc * NT > GX_COL_SF || p.T * nst > GX_MAX_STEPS || slabs > GX_MAX_SLABS) return B200_ENOTIMPL;
     p.nslot = std::min(slabs, 3);
     const int nsteps = p.T * nst;
     p.a_slot = ((uint32_t)p.R * 128u + 1023u) & ~1023u;
@@ -510,6 +533,16 @@ static int pick_nt(int M, int N) {
     return tiles_n * ((M + 127) / 128) <= nsm ? 128 : 256;
 }
 
+// Accumulators per tile.  The kernel can split a tile's k-blocks over 2 or 4 accumulators issued by two
+// warps (independent MMA chains); measured on B200 that buys nothing -- the steps are paced by the arrival
+// of the weight tiles, not by the MMA chain -- and it costs TMEM columns that are better spent on more tiles
+// per CTA, so one accumulator per tile it is.  B200_GX_NACC=2|4 switches the split on for experiments.
+static int gx_accumulators(int NT) {
+    static const int forced = [] { const char* e = getenv("B200_GX_NACC"); return e ? atoi(e) : 1; }();
+    if ((forced == 2 || forced == 4) && forced * NT <= GX_COL_SF) return forced;
+    return 1;
+}
+
 // Consecutive weight-row tiles per CTA: as many as the accumulator columns (T * NT <= 256), the per-step
 // barriers (T * K/256 <= 64) and the scale slabs allow while the launch still has a CTA for every SM.  A
 // CTA pays its set-up (TMEM, barriers, descriptors, pipeline fill and drain) once for all its tiles.
@@ -518,7 +551,7 @@ static int pick_tiles_per_cta(int NT, int K, int tiles_n, long jobs) {
     scale_box(K, &box, &swz);
     const int nst = K / 256, slabs_per_tile = swz ? nst / 8 : 1, nsm = sm_count();
     int best = 1;
-    for (int T = 2; T <= tiles_n && T * NT <= GX_COL_SF && T * nst <= GX_MAX_STEPS && T * slabs_per_tile <= GX_MAX_SLABS; ++T)
+    for (int T = 2; T <= tiles_n && T * gx_accumulators(NT) * NT <= GX_COL_SF && T * nst <= GX_MAX_STEPS && T * slabs_per_tile <= GX_MAX_SLABS; ++T)
         if (jobs * ((tiles_n + T - 1) / T) >= nsm) best = T;
     return best;
 }
