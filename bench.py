@@ -201,26 +201,30 @@ def bench_siblings(P, M, steps, warmup, copies, sampler_index=None):
 
 
 def bench_siblings_e2e(P, state, steps, warmup):
-    """Host buffers: x from pinned memory in, the six outputs (one device buffer) back to pinned memory, per step."""
+    """Host buffers: x from pinned memory in, the six outputs (one device buffer) back to pinned memory, a
+    stream synchronisation per step.  The loop itself is C++ against the C ABI (tests/cpp/e2e_loop.cu), the way
+    an engine like the reference's calls this path; Python only hands over the pointers."""
+    import ctypes as C
     sets, x, ys, jobs, ybuf = state
-    M = x.shape[0]
+    M, n = x.shape[0], len(SIBLINGS)
+    path = os.path.join(ROOT, 'tests', 'cpp', 'libe2e_loop.so')
+    if not os.path.exists(path):
+        raise SystemExit('tests/cpp/libe2e_loop.so is missing: run __graft_entry__.build()')
+    L = C.CDLL(path)
+    L.e2e_gemv_multi_loop.restype = C.c_double
     xh = torch.randn((M, K_HID)).pin_memory()
     yh = torch.empty(ybuf.shape).pin_memory()
+    rot = (P.GemvJob * (len(jobs) * n))()
+    for c, j in enumerate(jobs):
+        for i in range(n):
+            rot[c * n + i] = j[i]
+    rc = C.c_int(0)
     s = torch.cuda.current_stream()
-
-    def step(i):
-        x.copy_(xh, non_blocking=True)
-        P.gemv_multi(sets[i % len(sets)], x, M, ys, jobs=jobs[i % len(sets)])
-        yh.copy_(ybuf, non_blocking=True)
-        s.synchronize()                            # the caller reads the result every step
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for i in range(steps):
-        step(i)
-    torch.cuda.synchronize()
-    ms = (time.perf_counter() - t0) * 1e3 / steps
+    ms = L.e2e_gemv_multi_loop(rot, len(jobs), n, M, K_HID, C.c_void_p(xh.data_ptr()), C.c_void_p(x.data_ptr()), C.c_size_t(M * K_HID * 4),
+                               C.c_void_p(ybuf.data_ptr()), C.c_void_p(yh.data_ptr()), C.c_size_t(ybuf.numel() * 4),
+                               int(steps), int(warmup), C.c_void_p(s.cuda_stream), C.byref(rc))
+    if rc.value:
+        raise SystemExit('end-to-end loop failed: status %d' % rc.value)
     return ms, M * K_HID * 4, M * sum(SIBLINGS) * 4
 
 
@@ -561,6 +565,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--quick', action='store_true', help='headline only, no sub-workloads')
     ap.add_argument('--ep-tokens', default='256,2048', help='token counts of the expert-parallel workload')
+    ap.add_argument('--gemm-shapes', default='12288x32,12288x128,12288x512,4096x32,4096x128,4096x512', help='NxM list of the prefill GEMM sub-workloads')
     ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,lm_head,siblings,gemm,dense_mlp,kda,moe,moe_prefill,ep,quant)')
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
@@ -654,8 +659,8 @@ def main():
                                        'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
     if want('gemm'):
         fp4_peak = 4 * 1652.6                        # dense FP4 tensor peak taken as 4x the measured bf16 burst (TFLOP/s)
-        for N in (12288, 4096):
-            for M in (32, 128, 512):
+        for N, M in [tuple(int(v) for v in sh.split('x')) for sh in a.gemm_shapes.split(',') if sh]:
+            if True:
                 m, fl, b, dev_exact = bench_gemm_wide(P, N, M, max(20, sub_steps // 5), a.warmup)
                 sub['gemm_bf16_%dx4096_M%d' % (N, M)] = {
                     'us': m * 1e3, 'min_us': LAST_TIMING['min_ms_per_step'] * 1e3, 'tflops': fl / (m * 1e-3) / 1e12,

@@ -63,6 +63,8 @@ def lib():
         L.b200_nvfp4_version.restype = ci
         L.b200_nvfp4_device_status.argtypes = [C.POINTER(C.c_uint), ci]
         L.b200_nvfp4_selftest_bounded_wait.argtypes = [vp]
+        L.b200_nvfp4_set_byte_credit.argtypes = [vp, vp]
+        L.b200_nvfp4_flush_byte_credit.argtypes = [ci]
         L.b200_nvfp4_gemm.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, ci, vp]
         L.b200_nvfp4_gemv_multi.argtypes = [C.POINTER(GemvJob), ci, ci, ci, ci, vp]
         L.b200_nvfp4_split_workspace_bytes.restype = st; L.b200_nvfp4_split_workspace_bytes.argtypes = [ci, ci]
@@ -103,7 +105,7 @@ def lib():
 
 
 ENOTIMPL = 6
-EXPORTS = ['b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_selftest_bounded_wait', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
+EXPORTS = ['b200_nvfp4_set_byte_credit', 'b200_nvfp4_flush_byte_credit', 'b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_selftest_bounded_wait', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
            'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_dense_mlp_workspace_bytes', 'b200_dense_mlp', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
            'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release',
@@ -462,3 +464,24 @@ class Overlay:
     def close(self):
         check(lib().b200_overlay_close(self.h), 'b200_overlay_close')
         self.h = C.c_void_p(0)
+
+
+CREDIT_FN = C.CFUNCTYPE(None, C.c_int, C.c_double, C.c_void_p)
+
+
+class ByteCredit:
+    """Collects the weight bytes the library reports per launch site (b200_nvfp4_set_byte_credit)."""
+
+    def __init__(self):
+        self.by_kind = {}
+        self._cb = CREDIT_FN(lambda kind, nbytes, user: self.by_kind.__setitem__(kind, self.by_kind.get(kind, 0.0) + nbytes))
+
+    def __enter__(self):
+        check(lib().b200_nvfp4_set_byte_credit(C.cast(self._cb, C.c_void_p), None), 'b200_nvfp4_set_byte_credit')
+        return self
+
+    def flush(self, credit=True):
+        check(lib().b200_nvfp4_flush_byte_credit(1 if credit else 0), 'b200_nvfp4_flush_byte_credit')
+
+    def __exit__(self, *a):
+        check(lib().b200_nvfp4_set_byte_credit(None, None), 'b200_nvfp4_set_byte_credit')

@@ -38,6 +38,14 @@ bool tmap_available();
 bool tmap_u8_2d(void* out, const void* base, size_t rows, size_t row_bytes, int box_bytes, int box_rows, bool swz, bool cached);
 bool scale_box(int K, int* box, int* swz);
 
+// common.cu: byte accounting (b200_nvfp4_set_byte_credit).  credit(): host-known counts; the grouped MoE paths
+// add their job counts on the device to credit_counters()[0] (gate and up jobs) and [1] (down jobs), each job
+// being one pass over one expert matrix; geometry of the last grouped call is remembered for the flush.
+void credit(int kind, double bytes);
+bool credit_on();
+unsigned long long* credit_counters();
+void credit_grouped_geometry(int hidden, int inter);
+
 // gemv.cu
 int nvfp4_multi(const b200_gemv_job* jobs, int n, int M, int K, cudaStream_t s, void* split_ws);
 int dense_gemm(float* y, const void* W, const float* x, int M, int N, int K, int dtype, cudaStream_t s);

@@ -55,6 +55,27 @@ int prefill_fp4_option() {
     return g_prefill_fp4;
 }
 
+// ---- byte accounting ---------------------------------------------------------------------------------
+static b200_byte_credit_fn g_credit_fn = nullptr;
+static void* g_credit_user = nullptr;
+static double g_grouped_matrix_bytes = 0.0;         // bytes of one expert matrix of the last grouped MoE call
+__device__ unsigned long long g_credit_jobs[2] = {0ull, 0ull};
+
+bool credit_on() { return g_credit_fn != nullptr; }
+void credit(int kind, double bytes) { if (g_credit_fn) g_credit_fn(kind, bytes, g_credit_user); }
+void credit_grouped_geometry(int hidden, int inter) { g_grouped_matrix_bytes = (double)hidden * inter * 0.5625; }
+unsigned long long* credit_counters() {
+    static unsigned long long* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_credit_jobs) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<unsigned long long*>(p);
+    }
+    return cache[dev];
+}
+
 int launch_failed(const char* what) {
     const cudaError_t e = cudaGetLastError();
     fprintf(stderr, "b200_nvfp4: %s failed: %s\n", what, cudaGetErrorString(e));
@@ -85,7 +106,25 @@ extern "C" const char* b200_nvfp4_strerror(int code) {
     }
 }
 
-extern "C" int b200_nvfp4_version(void) { return 100; }
+extern "C" int b200_nvfp4_version(void) { return 200; }
+
+extern "C" int b200_nvfp4_set_byte_credit(b200_byte_credit_fn fn, void* user) {
+    b200::g_credit_fn = fn; b200::g_credit_user = user;
+    return B200_OK;
+}
+
+extern "C" int b200_nvfp4_flush_byte_credit(int credit) {
+    unsigned long long* p = b200::credit_counters();
+    if (!p) return B200_ELAUNCH;
+    unsigned long long jobs[2] = {0ull, 0ull};
+    if (cudaMemcpy(jobs, p, sizeof jobs, cudaMemcpyDeviceToHost) != cudaSuccess || cudaMemset(p, 0, sizeof jobs) != cudaSuccess)
+        return b200::launch_failed("flush_byte_credit");
+    if (credit) {
+        b200::credit(B200_CREDIT_MOE_ACT, (double)jobs[0] * b200::g_grouped_matrix_bytes);
+        b200::credit(B200_CREDIT_MOE_DOWN, (double)jobs[1] * b200::g_grouped_matrix_bytes);
+    }
+    return B200_OK;
+}
 
 extern "C" int b200_nvfp4_set_option(int option, int value) {
     if (option == B200_OPT_STABLE_WEIGHTS) { b200::set_stable_weights(value); return B200_OK; }

@@ -583,6 +583,7 @@ int gemm_mxf4_dense(float* y, const b200_wref* W, const void* x, int x_kind, int
     if (!tmap_u8_2d(&mw, W->packed, (size_t)N, (size_t)K / 2, 128, R, true, true) ||
         !tmap_u8_2d(&ms, W->scale, (size_t)N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0, true) ||
         !tmap_u8_2d(&mx, xq, (size_t)M, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
+    credit(B200_CREDIT_GEMM, (double)n_jobs * N * K * 0.5625);      // W streams once per token tile (the later tiles mostly from L2)
     if (int rc = quant_act_launch(x_kind ? 1 : 0, x, nullptr, 0.f, nullptr, nullptr, M, n_jobs * NT, K, xq, sfb, rows, gsx, s)) return rc;
     const int tiles_n = (N + R - 1) / R;
     p.T = pick_tiles_per_cta(NT, K, tiles_n, n_jobs);

@@ -465,7 +465,13 @@ using namespace b200;
 extern "C" int b200_nvfp4_gemm(float* y, const b200_wref* W, const float* x, int M, int N, int K,
                                int dtype, b200_stream stream) {
     if (!W || M < 1) return B200_EINVAL;
-    if (!W->packed) return dense_gemm(y, W->p, x, M, N, K, dtype, stream);
+    if (!W->packed) {
+        // one pass per 8 rows, or a single one through the many-row kernel (same conditions as dense_gemm)
+        const bool one = M > 8 && dtype == B200_BF16 && N <= 2048 && K >= 2048;
+        credit(B200_CREDIT_GEMM, (double)(one ? 1 : (M + 7) / 8) * N * K * (dtype == B200_F32 ? 4.0 : 2.0));
+        return dense_gemm(y, W->p, x, M, N, K, dtype, stream);
+    }
+    credit(B200_CREDIT_GEMM, (double)((M + B200_GEMV_M_MAX - 1) / B200_GEMV_M_MAX) * N * K * 0.5625);
     for (int done = 0; done < M;) {
         const int c = std::min(M - done, (int)B200_GEMV_M_MAX);
         b200_gemv_job j{y + (size_t)done * N, *W, x + (size_t)done * K, N};
@@ -490,6 +496,7 @@ extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, 
         const int rc = gemm_mxf4_dense(y, W, x, 1, M, N, K, ws, stream);
         if (rc != B200_ENOTIMPL) return rc;
     }
+    credit(B200_CREDIT_GEMM, (double)((M + B200_GEMV_M_MAX - 1) / B200_GEMV_M_MAX) * N * K * 0.5625);
     // every row at once: one split launch, then one pass over the weights per 8 rows
     b200_gemv_job j{y, *W, x, N};
     GemvParams p{};
@@ -499,7 +506,13 @@ extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, 
     for (int i = 1; i < B200_GEMV_MULTI_MAX; ++i) { p.j[i] = p.j[0]; p.j[i].N = 0; p.j[i].task0 = 0x7fffffff; }
     const int rc = nvfp4_multi_umma_ws(p, M, ws, stream);
     if (rc != B200_ENOTIMPL) return rc;
-    return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
+    for (int done = 0; done < M;) {                   // as b200_nvfp4_gemm, whose bytes were credited above
+        const int c = std::min(M - done, (int)B200_GEMV_M_MAX);
+        b200_gemv_job jj{y + (size_t)done * N, *W, x + (size_t)done * K, N};
+        if (int r2 = nvfp4_multi(&jj, 1, c, K, stream, nullptr)) return r2;
+        done += c;
+    }
+    return B200_OK;
 }
 
 extern "C" int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M, int K, int dtype,
@@ -508,6 +521,11 @@ extern "C" int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M,
     if (ws && ((uintptr_t)ws & 255)) return B200_EALIGN;
     for (int i = 0; i < n; ++i)
         if (!jobs[i].W.packed) return b200_nvfp4_gemv_multi(jobs, n, M, K, dtype, stream);
+    if (credit_on()) {
+        double b = 0.0;
+        for (int i = 0; i < n; ++i) b += (double)jobs[i].N * K * 0.5625;
+        credit(B200_CREDIT_GEMM, b);
+    }
     return nvfp4_multi(jobs, n, M, K, stream, ws);
 }
 
@@ -516,6 +534,11 @@ extern "C" int b200_nvfp4_gemv_multi(const b200_gemv_job* jobs, int n, int M, in
     if (!jobs || n < 1 || n > B200_GEMV_MULTI_MAX || M < 1 || M > B200_GEMV_M_MAX) return B200_EINVAL;
     bool all_q = true;
     for (int i = 0; i < n; ++i) all_q = all_q && jobs[i].W.packed != nullptr;
+    if (all_q && credit_on()) {
+        double b = 0.0;
+        for (int i = 0; i < n; ++i) b += (double)jobs[i].N * K * 0.5625;
+        credit(B200_CREDIT_GEMM, b);
+    }
     if (all_q) return nvfp4_multi(jobs, n, M, K, stream, nullptr);
     for (int i = 0; i < n; ++i) {                  // mixed or plain weights: correct, not fused
         const int rc = b200_nvfp4_gemm(jobs[i].y, &jobs[i].W, jobs[i].x, M, jobs[i].N, K, dtype, stream);

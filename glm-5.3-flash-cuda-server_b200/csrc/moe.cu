@@ -201,6 +201,8 @@ static int experts_forward(const float* x, const b200_moe_layer* L, float* y, co
         const int rc = moe_umma_experts(x, L, y, sel, wts, act, M, s, planned, wide);
         if (rc != B200_ENOTIMPL) return rc;
     }
+    credit(B200_CREDIT_MOE_ACT, (double)M * (L->topk + (L->shared ? 1 : 0)) * 2.0 * L->inter * L->hidden * 0.5625);
+    credit(B200_CREDIT_MOE_DOWN, (double)M * (L->topk + (L->shared ? 1 : 0)) * 1.0 * L->inter * L->hidden * 0.5625);
     MoeArgs a{};
     a.x = x; a.y = y; a.sel = sel; a.wts = wts; a.act = act;
     a.experts = L->experts; a.shared = L->shared;

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(1024)
 k_moe_group(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int* __restrict__ posof,
             const float* __restrict__ xg, SplitJob* __restrict__ s1, SplitJob* __restrict__ s2,
             unsigned char* __restrict__ img1, unsigned char* __restrict__ img2, float* __restrict__ gam1,
-            float* __restrict__ gam2, int M, int max_jobs) {
+            float* __restrict__ gam2, int M, int max_jobs, unsigned long long* __restrict__ credit_jobs) {
     __shared__ int cnt[MG_MAX_GROUPS], off[MG_MAX_GROUPS], jstart[MG_MAX_GROUPS], cursor[MG_MAX_GROUPS];
     __shared__ int total_jobs;
     const int G = q.E + 1, pairs = M * q.ns;
@@ -126,6 +126,7 @@ k_moe_group(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, 
         int o = 0, j = 0;
         for (int e = 0; e < G; ++e) { off[e] = o; jstart[e] = j; o += cnt[e]; j += (cnt[e] + 7) >> 3; }
         total_jobs = j;
+        if (credit_jobs) { atomicAdd(&credit_jobs[0], 2ull * j); atomicAdd(&credit_jobs[1], (unsigned long long)j); }   // passes over expert matrices: gate + up, down
     }
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -234,7 +235,8 @@ static int moe_umma_grouped(const float* x, const b200_moe_layer* L, float* y, c
     q.ubuf = reinterpret_cast<float*>(w);
     q.experts = L->experts; q.shared = L->shared; q.maps = P->maps; q.x = x;
     q.topk = L->topk; q.ns = ns; q.E = L->n_expert; q.H = H; q.I = I;
-    k_moe_group<<<1, 1024, 0, s>>>(q, sel, posof, xg, s1, s2, img1, img2, gam1, gam2, M, max_jobs);
+    if (credit_on()) credit_grouped_geometry(H, I);
+    k_moe_group<<<1, 1024, 0, s>>>(q, sel, posof, xg, s1, s2, img1, img2, gam1, gam2, M, max_jobs, credit_on() ? credit_counters() : nullptr);
     if (int rc = check_launch("k_moe_group")) return rc;
     const size_t n4 = (size_t)pairs * (H >> 2);
     k_moe_gather<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(xg, x, posof, pairs, ns, H);
@@ -256,7 +258,8 @@ static int moe_umma_grouped(const float* x, const b200_moe_layer* L, float* y, c
 __global__ void __launch_bounds__(1024)
 k_moe_group_gx(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int* __restrict__ posof,
                int* __restrict__ src_row, GxJob* __restrict__ j1, GxJob* __restrict__ j2,
-               const float* __restrict__ gsx1, const float* __restrict__ gsx2, int M, int NT, int max_jobs) {
+               const float* __restrict__ gsx1, const float* __restrict__ gsx2, int M, int NT, int max_jobs,
+               unsigned long long* __restrict__ credit_jobs) {
     __shared__ int cnt[MG_MAX_GROUPS], off[MG_MAX_GROUPS], jstart[MG_MAX_GROUPS], cursor[MG_MAX_GROUPS];
     __shared__ int total_jobs;
     pdl_wait();
@@ -275,6 +278,7 @@ k_moe_group_gx(const __grid_constant__ MoePlan q, const int32_t* __restrict__ se
         int o = 0, j = 0;
         for (int e = 0; e < G; ++e) { off[e] = o; jstart[e] = j; o += cnt[e]; j += (cnt[e] + NT - 1) / NT; }
         total_jobs = j;
+        if (credit_jobs) { atomicAdd(&credit_jobs[0], 2ull * j); atomicAdd(&credit_jobs[1], (unsigned long long)j); }   // passes over expert matrices: gate + up, down
     }
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -337,7 +341,8 @@ static int moe_gx_grouped(const float* x, const b200_moe_layer* L, float* y, con
     q.part = reinterpret_cast<float*>(w);
     q.experts = L->experts; q.shared = L->shared; q.maps = P->maps; q.x = x;
     q.topk = L->topk; q.ns = ns; q.E = L->n_expert; q.H = H; q.I = I;
-    k_moe_group_gx<<<1, 1024, 0, s>>>(q, sel, posof, src_row, j1, j2, gs1, gs2, M, NT, max_jobs);
+    if (credit_on()) credit_grouped_geometry(H, I);
+    k_moe_group_gx<<<1, 1024, 0, s>>>(q, sel, posof, src_row, j1, j2, gs1, gs2, M, NT, max_jobs, credit_on() ? credit_counters() : nullptr);
     if (int rc = check_launch("k_moe_group_gx")) return rc;
     if (int rc = quant_act_launch(1, x, nullptr, 0.f, src_row, nullptr, pairs, pairs, H, xq1, sf1, padrows, gs1, s)) return rc;
     // jobs the table is likely to hold: every expert that can be hit once, plus the extra chunks of busy experts
@@ -364,6 +369,8 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
     int R_gu = 0, R_d = 0;
     if (int rc = moe_umma_plan_args(x, L, scratch, M, &q, &R_gu, &R_d)) return rc;
     const int pairs = M * q.ns;
+    credit(B200_CREDIT_MOE_ACT, (double)pairs * 2.0 * q.I * q.H * 0.5625);      // every pair streams its expert (reference kernels/moe.cu:719-722)
+    credit(B200_CREDIT_MOE_DOWN, (double)pairs * 1.0 * q.I * q.H * 0.5625);
     if (!planned) {
         k_moe_plan<<<(pairs + 127) / 128, 128, 0, s>>>(q, sel, M);
         if (int rc = check_launch("k_moe_plan")) return rc;

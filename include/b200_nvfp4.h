@@ -111,6 +111,23 @@ int b200_nvfp4_selftest_bounded_wait(b200_stream stream);
 enum { B200_OPT_STABLE_WEIGHTS = 1, B200_OPT_PREFILL_FP4 = 2 };
 int b200_nvfp4_set_option(int option, int value);
 
+/* Byte accounting for a host-side profiler.  The reference's launch sites credit the weight bytes they
+ * read to its profiler (dprof_bytes: kernels/gemv.cu:377, 427, 458, 677; kernels/moe.cu:656-667, 719-722;
+ * include/dprof.h:83-103), because a weight read at width M serves M tokens and the MoE count depends on
+ * the routing.  This library reports the same quantity through a callback: `fn(kind, bytes, user)` is
+ * called on the calling host thread at every launch site with the weight bytes THAT call reads -- for an
+ * NVFP4 product passes * N * K * 0.5625 (passes = how often this library streams W for the call's M),
+ * for the MoE experts up to 8 tokens pairs * 3 * inter * hidden * 0.5625 split into its gate/up and
+ * down halves.  Where rows are grouped by expert on the device (more than 8 tokens) the count is only
+ * known there: it accumulates in a device counter that b200_nvfp4_flush_byte_credit reads (this
+ * SYNCHRONISES), credits (credit != 0) or discards (credit == 0, after a warm-up), and clears -- the
+ * contract of the reference's dprof_set_flush.  A drop-in build's callback simply forwards to dprof_bytes /
+ * dprof_bytes_to.  NULL switches the reporting off (the default). */
+enum { B200_CREDIT_GEMM = 0, B200_CREDIT_MOE_ROUTER = 1, B200_CREDIT_MOE_ACT = 2, B200_CREDIT_MOE_DOWN = 3 };
+typedef void (*b200_byte_credit_fn)(int kind, double bytes, void* user);
+int b200_nvfp4_set_byte_credit(b200_byte_credit_fn fn, void* user);
+int b200_nvfp4_flush_byte_credit(int credit);
+
 /* y[M,N] = x[M,K] . W[N,K]^T.  Replaces glm5::gemm / glm5::gemv (reference include/gemv.h:29,
  * 75; kernels/gemv.cu:369-396, 456-465, 649-701).  Any M >= 1: rows are processed in chunks of
  * up to 8 and W is re-read once per chunk.  Each output row of y depends only on its own row

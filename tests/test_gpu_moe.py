@@ -332,3 +332,37 @@ def test_router_of_a_batch_equals_router_of_each_token_bitwise():
         assert torch.equal(l1[0], logits[m]) and torch.equal(s1[0], sel[m]) and torch.equal(w1[0], wts[m]), m
     s8, w8, l8 = P.moe_route(layer, x[:8].contiguous())
     assert torch.equal(l8, logits[:8])
+
+
+def test_byte_credit_reports_what_each_call_streams():
+    """The profiler hook: host-known counts at the launch sites, device-side job counts after a flush
+    (the contract of the reference's dprof_bytes / dprof_set_flush, include/dprof.h:83-103)."""
+    P = pkg()
+    H, I, E, topk = 1024, 512, 16, 2
+    layer, d = build_layer(H, I, E, topk, seed=11)
+    W = P.Nvfp4Weight(*host_triple((300, 1024), 5))
+    per = I * H * 0.5625
+    with P.ByteCredit() as bc:
+        P.gemm(W, torch.randn(1, 1024, device='cuda'))
+        assert bc.by_kind == {0: 300 * 1024 * 0.5625}
+        P.gemm(W, torch.randn(20, 1024, device='cuda'))                  # three passes of up to 8 rows
+        assert bc.by_kind[0] == 4 * 300 * 1024 * 0.5625
+        bc.by_kind.clear()
+        P.moe_forward(layer, torch.randn(3, H, device='cuda'))           # CUDA-core experts: every pair streams its expert
+        assert bc.by_kind[2] == 3 * (topk + 1) * 2 * per and bc.by_kind[3] == 3 * (topk + 1) * per
+        assert bc.by_kind[0] == E * H * 2.0                              # the bf16 router
+        assert P.moe_prepare(layer)
+        try:
+            bc.by_kind.clear()
+            x = torch.randn(40, H, device='cuda')
+            _, sel, _ = P.moe_forward(layer, x)                          # grouped on the device: known after the flush
+            assert 2 not in bc.by_kind
+            bc.flush()
+            distinct = len(set(sel.cpu().numpy().ravel().tolist())) + 1
+            jobs = bc.by_kind[3] / per
+            assert distinct <= jobs <= distinct + 40 * (topk + 1) / 32 and bc.by_kind[2] == 2 * bc.by_kind[3]
+            bc.by_kind.clear()
+            P.moe_forward(layer, x); bc.flush(credit=False); bc.flush()  # a discarded warm-up is not billed later
+            assert bc.by_kind.get(3, 0.0) == 0.0
+        finally:
+            P.moe_release(layer)
