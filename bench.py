@@ -566,6 +566,7 @@ def main():
     ap.add_argument('--quick', action='store_true', help='headline only, no sub-workloads')
     ap.add_argument('--ep-tokens', default='256,2048', help='token counts of the expert-parallel workload')
     ap.add_argument('--gemm-shapes', default='12288x32,12288x128,12288x512,4096x32,4096x128,4096x512', help='NxM list of the prefill GEMM sub-workloads')
+    ap.add_argument('--profile', default='', help='run ONE small workload a few times and exit (for ncu captures): siblings, gemm_NxM, quant, moe_mM, moe_prefill_mM')
     ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,lm_head,siblings,gemm,dense_mlp,kda,moe,moe_prefill,ep,quant)')
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
@@ -584,6 +585,8 @@ def main():
     torch.cuda.set_device(local)
     P.lib()                                            # fail now if the library is missing
     P.set_option(P.OPT_STABLE_WEIGHTS, 1)              # weights are loaded once, as in the engine
+    if a.profile:
+        return profile_mode(P, a.profile)
     if world > 1:
         # The headline path does not shard (every gemv is an independent unit: replicas only), so each
         # rank runs the headline workload on its own GPU and the line reports the sum; the one part of
@@ -724,6 +727,42 @@ def main():
     print(json.dumps(out))
     if any(not r['parity_ok'] for r in ep.values()):
         raise SystemExit('expert-parallel parity failed: %s' % {k: r['parity'] for k, r in ep.items()})
+
+
+def profile_mode(P, name):
+    """One workload, a few plain launches, no timing and no graphs: the command ncu captures are taken from
+    (the summaries under profiles/ name the exact command line)."""
+    reps = 3
+    if name == 'siblings':
+        Ws = [make_weight(P, n, K_HID, 1000 + i)[0] for i, n in enumerate(SIBLINGS)]
+        x = torch.randn((1, K_HID), device='cuda')
+        for _ in range(reps):
+            P.gemv_multi(Ws, x, 1)
+    elif name.startswith('gemm_'):
+        N, M = (int(v) for v in name[5:].split('x'))
+        Ws = [make_weight(P, N, K_HID, 998 + i)[0] for i in range(reps)]          # a fresh weight per launch
+        x = torch.randn((M, K_HID), device='cuda').to(torch.bfloat16)
+        y = torch.empty((M, N), device='cuda'); ws = P.gemm_bf16_workspace(M, K_HID, x.device)
+        for W in Ws:
+            P.gemm_bf16(W, x, y, ws)
+    elif name == 'quant':
+        ws = [(torch.randn((12288, K_HID), device='cuda') * 0.02).to(torch.bfloat16) for _ in range(2)]
+        out = None
+        for w in ws:
+            out = P.quantize(w, out=out)
+    elif name.startswith('moe_'):
+        prefill = name.startswith('moe_prefill_m')
+        M = int(name.split('_m')[-1])
+        layers = build_moe_layers(P, 2, 4096, 1536, 144, 8, 4100, zipf=prefill)
+        for L in layers:
+            P.moe_prepare(L)
+        x = torch.randn((M, 4096), device='cuda', generator=torch.Generator(device='cuda').manual_seed(77))
+        for i in range(reps):
+            P.moe_forward(layers[i % 2], x)
+    else:
+        raise SystemExit('unknown --profile workload: ' + name)
+    torch.cuda.synchronize()
+    print(json.dumps({'profile': name, 'device_status': P.device_status()}))
 
 
 def reference_arm(a, P, rank, peak):
