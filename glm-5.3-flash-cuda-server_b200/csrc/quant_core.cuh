@@ -25,11 +25,16 @@ __device__ __forceinline__ int e4m3_floor_code(float s) {
     return (int)((((b >> 23) - 120u) << 3) | ((b >> 20) & 7u));
 }
 
-__device__ __forceinline__ int e2m1_index(float a) {          // #{mid < a}, mids of the e2m1 grid
-    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
-}
-
-// One 16-group: scale code and sixteen e2m1 codes, fp32 IEEE operations in the reference's order.
+// One 16-group: scale code and sixteen e2m1 codes, bit for bit what the reference's fp32 operations give.
+//
+// The reference computes q = fl(v / eff) per element and counts the e2m1 mid-points strictly below |q|.
+// A correctly rounded division per element is what made this kernel instruction-bound, so the count is
+// taken without dividing: fl(|v| / eff) > mid  <=>  |v| / eff > mid + ulp(mid)/2 in real arithmetic (all
+// seven mid-points have even mantissas, so an exact tie rounds back down to the mid-point)  <=>
+// |v| > eff * (mid + ulp(mid)/2), and that product of a 24-bit and a 25-bit number is exact in double.
+// Rounded DOWN to fp32 it is a threshold t with  |v| > t  <=>  the reference's comparison, for every fp32 v
+// (an infinity exceeds every threshold, a NaN none: as v / eff would).  Seven thresholds per group, then
+// seven comparisons per element.
 __device__ __forceinline__ void quantize_group(const float (&v)[16], float gs, uint32_t& lo, uint32_t& hi, int& code) {
     float amax = 0.f;
     #pragma unroll
@@ -42,12 +47,19 @@ __device__ __forceinline__ void quantize_group(const float (&v)[16], float gs, u
         code += (mid < s) ? 1 : 0;
     }
     const float eff = fmaxf(__fdiv_rn(e4m3_to_f32(code), gs), 1e-30f);
+    // mid-points 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5 plus half an ulp of their binade (2^-26 .. 2^-22)
+    const double de = (double)eff;
+    const float t0 = __double2float_rd(de * (0.25 + 0x1p-26)), t1 = __double2float_rd(de * (0.75 + 0x1p-25)),
+                t2 = __double2float_rd(de * (1.25 + 0x1p-24)), t3 = __double2float_rd(de * (1.75 + 0x1p-24)),
+                t4 = __double2float_rd(de * (2.5 + 0x1p-23)), t5 = __double2float_rd(de * (3.5 + 0x1p-23)),
+                t6 = __double2float_rd(de * (5.0 + 0x1p-22));
     lo = 0; hi = 0;
     #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const float q = __fdiv_rn(v[j], eff);
-        uint32_t c = (uint32_t)e2m1_index(fabsf(q));
-        if (c != 0 && (__float_as_uint(q) >> 31)) c |= 8u;
+        const float a = fabsf(v[j]);
+        // number of thresholds below a, by bisection (the thresholds increase): three comparisons per element
+        uint32_t c = a > t3 ? (a > t5 ? (a > t6 ? 7u : 6u) : (a > t4 ? 5u : 4u)) : (a > t1 ? (a > t2 ? 3u : 2u) : (a > t0 ? 1u : 0u));
+        if (c != 0 && (__float_as_uint(v[j]) >> 31)) c |= 8u;
         if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
     }
 }
