@@ -57,8 +57,7 @@ __device__ __forceinline__ void quantize_group(const float (&v)[16], float gs, u
     #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const float a = fabsf(v[j]);
-        // number of thresholds below a, by bisection (the thresholds increase): three comparisons per element
-        uint32_t c = a > t3 ? (a > t5 ? (a > t6 ? 7u : 6u) : (a > t4 ? 5u : 4u)) : (a > t1 ? (a > t2 ? 3u : 2u) : (a > t0 ? 1u : 0u));
+        uint32_t c = (uint32_t)((a > t0) + (a > t1) + (a > t2) + (a > t3) + (a > t4) + (a > t5) + (a > t6));
         if (c != 0 && (__float_as_uint(v[j]) >> 31)) c |= 8u;
         if (j < 8) lo |= c << (4 * j); else hi |= c << (4 * (j - 8));
     }
