@@ -135,6 +135,15 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         J.y += (size_t)J.row0 * J.ldy;
         J.gs_x += J.row0;
     }
+    // Jobs of a table launch with few rows load (and multiply) only a 32- or 64-row box of activations: an
+    // expert that three tokens chose should not pull a 128-row tile through L2 at every step.  In table
+    // mode the two weight-map parameters are unused and carry the activation maps with the smaller boxes.
+    int nb = NT;
+    const void* mx = &map_x;
+    if (p.table) {
+        if (NT > 32 && J.rows <= 32) { nb = 32; mx = &map_w; }
+        else if (NT > 64 && J.rows <= 64) { nb = 64; mx = &map_s; }
+    }
     // this CTA's consecutive tiles of R weight rows: [tile0, tile0 + ntile)
     const int tile0 = chunk * p.T, ntile = min(p.T, (J.N + R - 1) / R - tile0);
     if (ntile <= 0) return;
@@ -171,11 +180,11 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" :: "l"(mw) : "memory");
             asm volatile("prefetch.tensormap [%0];" :: "l"(ms) : "memory");
-            asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+            asm volatile("prefetch.tensormap [%0];" :: "l"(mx) : "memory");
         }
         if (!p.prefetch_before_wait) pdl_wait();
         const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), slab0 = smem_u32(&slab_bar[0]);
-        const uint32_t step_bytes = (uint32_t)R * 128u + NT * 128u + NT * 16u;
+        const uint32_t step_bytes = (uint32_t)R * 128u + (uint32_t)nb * 128u + (uint32_t)nb * 16u;
         int t = lane / nst, it = lane - t * nst;
         const int spt = nst / sps;                 // slabs per tile
         for (int g = lane; g < nsteps; g += 32) {
@@ -198,8 +207,8 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             gx_tma_2d(smem_u32(ringA) + (uint32_t)sA * p.a_slot, mw, it * 128, rown0, bar);     // weights may be read early (stable weights)
             pdl_wait();                                                           // the activations come from the quantiser launch
             if (g >= p.sb) mbar_wait_spin(empty0 + (g - p.sb) * 8, 0, p.status, 7);
-            gx_tma_2d(smem_u32(ringB) + (uint32_t)sB * B_BYTES, &map_x, it * 128, J.row0, bar);
-            bulk_g2s(smem_u32(sfbs) + (uint32_t)sB * NT * 16u, p.sfb + ((size_t)it * p.sfb_rows + (size_t)J.row0) * 16, NT * 16u, bar);
+            gx_tma_2d(smem_u32(ringB) + (uint32_t)sB * B_BYTES, mx, it * 128, J.row0, bar);
+            bulk_g2s(smem_u32(sfbs) + (uint32_t)sB * NT * 16u, p.sfb + ((size_t)it * p.sfb_rows + (size_t)J.row0) * 16, (uint32_t)nb * 16u, bar);
             it += 32; while (it >= nst) { it -= nst; ++t; }
         }
         __syncwarp();
@@ -216,7 +225,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
         // them up in a fixed order -- and with two or more of them two warps issue: warp 1 the even
         // k-blocks, warp 3 the odd ones (different accumulators, so no order between the warps matters).
         const int mwi = warp == 1 ? 0 : 1, two = p.nacc >= 2;
-        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(nb >> 3) << 17) | ((128u >> 4) << 24);
         const uint64_t dA0 = gx_desc(smem_u32(ringA)), dB0 = gx_desc(smem_u32(ringB));
         const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
         int sA = 0, sB = 0, sF = 0, t = 0, it = 0;
@@ -285,7 +294,7 @@ k_gemm_mxf4(const __grid_constant__ GxParams p, const __grid_constant__ CUtensor
             const unsigned char* sb = sfbs + (size_t)s * NT * 16;
             #pragma unroll
             for (int c = 0; c < CBS; ++c) {
-                const uint4 v = c < CB ? *reinterpret_cast<const uint4*>(sb + (size_t)(lane + 32 * c) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                const uint4 v = (c < CB && 32 * c < nb) ? *reinterpret_cast<const uint4*>(sb + (size_t)(lane + 32 * c) * 16) : make_uint4(0u, 0u, 0u, 0u);
                 rb[c] = v.x; rb[CBS + c] = v.y; rb[2 * CBS + c] = v.z; rb[3 * CBS + c] = v.w;
             }
             const uint32_t slot = tq + GX_COL_SF + (uint32_t)sf * SLOT;
@@ -604,11 +613,13 @@ int gemm_mxf4_table(const GxJob* table, int max_jobs, long expected_jobs, int NT
     if (!p.status) return B200_ENOTIMPL;
     p.n_jobs = max_jobs; p.K = K; p.R = R; p.prefetch_before_wait = 0;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
-    CUtensorMap mx;
-    if (!tmap_u8_2d(&mx, xq, x_rows, (size_t)K / 2, 128, NT, true, true)) return B200_ENOTIMPL;
+    CUtensorMap mx, mx32, mx64;                      // activation boxes of NT, 32 and 64 rows (jobs with few rows take the small ones)
+    if (!tmap_u8_2d(&mx, xq, x_rows, (size_t)K / 2, 128, NT, true, true) ||
+        !tmap_u8_2d(&mx32, xq, x_rows, (size_t)K / 2, 128, 32, true, true) ||
+        !tmap_u8_2d(&mx64, xq, x_rows, (size_t)K / 2, 128, 64, true, true)) return B200_ENOTIMPL;
     const int tiles_n = (N + R - 1) / R;
     p.T = pick_tiles_per_cta(NT, K, tiles_n, std::max(1L, expected_jobs));
-    return gx_launch(NT, p, mx, mx, mx, (tiles_n + p.T - 1) / p.T * max_jobs, s);
+    return gx_launch(NT, p, mx, mx32, mx64, (tiles_n + p.T - 1) / p.T * max_jobs, s);
 }
 
 }  // namespace b200
