@@ -316,7 +316,7 @@ extern "C" int b200_moe_forward(const float* x, const b200_moe_layer* L, float* 
 // callers the scratch lives inside the library, in the array below, which every GPU that loads
 // the library holds until the process exits.
 //
-// Limit: B200_MOE_STATIC_WS_BYTES (1 MiB) -- enough for 8 tokens at the reference geometry
+// Limit: B200_MOE_STATIC_WS_BYTES (1 MiB) -- enough for 14 tokens at the reference geometry
 // (144 experts, top-8 + shared, inter 2048: 74 304 B per token).  Larger requests are refused.
 // The array is shared by every call on the device and keeps the previous call's bytes.  Nothing
 // in it has to start at zero: every byte a launch reads was written earlier by the same call
@@ -357,9 +357,9 @@ extern "C" int b200_moe_forward_static(const float* x, const b200_moe_layer* L, 
                 need, M, B200_MOE_STATIC_WS_BYTES);
         return B200_ELIMIT;
     }
+    if (!x || !y || !sel || !wts) return B200_EINVAL;
     void* ws = nullptr;
     if (int rc = moe_static_ws_ptr(&ws)) return rc;
-    if (!x || !y || !sel || !wts) return B200_EINVAL;
     float* logits = static_cast<float*>(ws);
     if (int rc = b200_moe_route(x, L, sel, wts, logits, M, stream)) return rc;
     float* act = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)M * L->n_expert * 4, 256));

@@ -20,6 +20,7 @@
 #include "moe_plan.cuh"
 #include "tma_pipe.cuh"
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -27,6 +28,14 @@
 namespace b200 {
 
 constexpr int MU_MAX_TOKENS = 8;
+// Fewest tokens for which the (token, slot) pairs are sorted by expert, so that every distinct expert
+// (and the shared expert) is streamed once for up to 8 rows instead of once per pair (the reference's
+// gathered kernels, kernels/moe.cu:353-581).  Below it every pair is its own job.  B200_MOE_GROUP_MIN
+// overrides it for experiments.
+static int group_min_tokens() {
+    static const int v = [] { const char* e = getenv("B200_MOE_GROUP_MIN"); const int n = e ? atoi(e) : 0; return n >= 2 ? n : MU_MAX_TOKENS + 1; }();
+    return v;
+}
 
 struct Prepared {
     const b200_nvfp4_mat* experts; const b200_nvfp4_mat* shared;     // key
@@ -180,10 +189,11 @@ static int grouped_max_jobs(const b200_moe_layer* L, int M) { return (M * (L->to
 static size_t moe_gx_ws_bytes(const b200_moe_layer* L, int M);
 size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
     const size_t ns = (size_t)L->topk + 1, pairs = (size_t)M * ns;
+    size_t small = 0;
     if (M <= MU_MAX_TOKENS)
-        return std::max(moe_gx_ws_bytes(L, M), up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4));
+        small = std::max(moe_gx_ws_bytes(L, M), up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4));
     const size_t mj = (size_t)grouped_max_jobs(L, M);
-    return std::max(moe_gx_ws_bytes(L, M), up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
+    return std::max(std::max(small, moe_gx_ws_bytes(L, M)), up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
            up256(mj * (L->hidden >> 8) * 8192) + up256(mj * (L->inter >> 8) * 8192) +
            2 * up256(pairs * L->hidden * 4) + 2 * up256(pairs * L->inter * 4));
 }
@@ -191,7 +201,7 @@ size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
 // Fills `q` for a call on a prepared layer.  B200_ENOTIMPL: not prepared, too many tokens, or an
 // unaligned activation -> the caller runs the CUDA-core experts.
 int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, int M, MoePlan* q, int* R_gu, int* R_d) {
-    if (M > MU_MAX_TOKENS || ((uintptr_t)x & 15)) return B200_ENOTIMPL;
+    if (M > MU_MAX_TOKENS || M >= group_min_tokens() || ((uintptr_t)x & 15)) return B200_ENOTIMPL;
     Prepared Pc;
     if (!find_prepared(L, &Pc)) return B200_ENOTIMPL;
     const Prepared* P = &Pc;
@@ -364,7 +374,7 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
         const int rc = moe_gx_grouped(x, L, y, sel, wts, scratch, M, s);
         if (rc != B200_ENOTIMPL) return rc;
     }
-    if (M > MU_MAX_TOKENS) return moe_umma_grouped(x, L, y, sel, wts, scratch, M, s);
+    if (M >= group_min_tokens()) return moe_umma_grouped(x, L, y, sel, wts, scratch, M, s);
     MoePlan q{};
     int R_gu = 0, R_d = 0;
     if (int rc = moe_umma_plan_args(x, L, scratch, M, &q, &R_gu, &R_d)) return rc;

@@ -1,10 +1,15 @@
 /* b200_nvfp4.h -- C ABI of the B200 (sm_100a) NVFP4 weight-path library, libb200nvfp4.so.
  *
  * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its comment says
- * host; every call enqueues on `stream` and returns without synchronising.  Return value:
- * 0 on success, a B200_E* code otherwise (b200_nvfp4_strerror names it).  The library owns
- * no device memory, has no CPU fallback, and keeps no state between calls besides cached
- * device attributes.
+ * host; every call enqueues on `stream` and returns without synchronising unless its comment says
+ * otherwise.  Return value: 0 on success, a B200_E* code otherwise (b200_nvfp4_strerror names it).
+ * There is no CPU fallback.  Buffers belong to the caller; what the library itself holds is:
+ *   - cached device attributes and encoded TMA tensor maps of the weights it has seen (host memory)
+ *   - per GPU: the status word of the bounded waits, the job counters of the byte accounting, and
+ *     the 1 MiB static scratch of b200_moe_forward_static
+ *   - per prepared MoE layer: its tensor maps in device memory (b200_moe_prepare .. b200_moe_release)
+ *   - per expert-parallel context: its buffers, streams, events and NCCL communicator
+ *   - the process-wide options (b200_nvfp4_set_option) and the byte-credit callback
  *
  * NVFP4 tensor = three buffers (reference include/nvfp4.cuh:3-7):
  *   packed [N, K/2] u8, low nibble = even k;  scale [N, K/16] u8 fp8-e4m3;  gscale [1] f32
@@ -246,7 +251,7 @@ int b200_moe_experts(const float* x, const b200_moe_layer* L, float* y, const in
  * loop, and is illegal under stream capture).  The scratch is a 1 MiB array inside the library
  * (b200_moe_static_ws_limit()), held by every GPU that loads the library until exit; it holds the
  * router logits [M, n_expert] and the activations [M, topk + 1, inter] (f32, each part rounded up
- * to 256 bytes), and a layer / M that needs more is refused with B200_ELIMIT.  This entry point
+ * to 256 bytes: 14 tokens at the reference geometry), and a layer / M that needs more is refused with B200_ELIMIT.  This entry point
  * always runs the CUDA-core expert kernels, prepared layer or not.  The call allocates
  * nothing.  The FIRST call on each device looks the array's device address up
  * (cudaGetSymbolAddress) -- make that call before any stream capture.  All calls on a device

@@ -29,6 +29,11 @@ struct MoeLayer {
 };
 
 // Not in the reference: layer geometry used by every call below (defaults = reference constants).
+// This is the ONE piece of process-wide state behind this header (MoeLayer has no room for it and the
+// reference's callers do not pass it): set it once, before moe_workspace_floats /
+// moe_batch_workspace_floats are asked for a size -- a workspace sized under one geometry is too small
+// for a larger one, and the calls cannot check that (ws carries no size).  Callers that need several
+// geometries in one process use the C ABI, whose b200_moe_layer carries the geometry per layer.
 void moe_set_geometry(int hidden, int inter, float routed_scale, float swiglu_limit, bool norm_topk);
 // Not in the reference: once per layer after its tables are built (src/engine.cu:168-195 is the
 // place), so that moe_forward* run their experts on the tensor-core kernels.
