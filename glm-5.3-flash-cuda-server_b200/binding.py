@@ -73,6 +73,8 @@ def lib():
         L.b200_nvfp4_gemm_bf16_workspace_bytes.restype = st; L.b200_nvfp4_gemm_bf16_workspace_bytes.argtypes = [ci, ci]
         L.b200_nvfp4_gemm_bf16.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, vp, vp]
         L.b200_nvfp4_quantize_tokens.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
+        L.b200_nvfp4_gemm_bf16_exact_workspace_bytes.restype = st; L.b200_nvfp4_gemm_bf16_exact_workspace_bytes.argtypes = [ci, ci]
+        L.b200_nvfp4_gemm_bf16_exact.argtypes = [vp, C.POINTER(WRef), vp, ci, ci, ci, vp, vp]
         L.b200_dense_mlp_workspace_bytes.restype = st; L.b200_dense_mlp_workspace_bytes.argtypes = [ci, ci, ci]
         L.b200_dense_mlp.argtypes = [vp, C.POINTER(WRef), C.POINTER(WRef), C.POINTER(WRef), ci, ci, C.c_float, vp, vp, ci, vp]
         L.b200_f32_to_bf16.argtypes = [vp, vp, st, vp]
@@ -106,7 +108,7 @@ def lib():
 
 ENOTIMPL = 6
 EXPORTS = ['b200_nvfp4_set_byte_credit', 'b200_nvfp4_flush_byte_credit', 'b200_nvfp4_strerror', 'b200_nvfp4_version', 'b200_nvfp4_device_status', 'b200_nvfp4_selftest_bounded_wait', 'b200_nvfp4_set_option', 'b200_nvfp4_gemm', 'b200_nvfp4_gemv_multi', 'b200_nvfp4_split_workspace_bytes', 'b200_nvfp4_gemm_ws', 'b200_nvfp4_gemv_multi_ws',
-           'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_dense_mlp_workspace_bytes', 'b200_dense_mlp', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
+           'b200_nvfp4_gemm_bf16_workspace_bytes', 'b200_nvfp4_gemm_bf16', 'b200_nvfp4_quantize_tokens', 'b200_nvfp4_gemm_bf16_exact_workspace_bytes', 'b200_nvfp4_gemm_bf16_exact', 'b200_dense_mlp_workspace_bytes', 'b200_dense_mlp', 'b200_f32_to_bf16', 'b200_bf16_to_f32', 'b200_nvfp4_quantize', 'b200_nvfp4_dequantize',
            'b200_moe_workspace_bytes', 'b200_moe_route', 'b200_moe_forward', 'b200_moe_experts',
            'b200_moe_forward_static', 'b200_moe_static_ws_limit', 'b200_moe_prepare', 'b200_moe_release',
            'b200_overlay_writer_open', 'b200_overlay_writer_add', 'b200_overlay_writer_close', 'b200_overlay_family',
@@ -203,6 +205,19 @@ def gemm_bf16(W, x_bf16, y=None, ws=None, stream=None):
         ws = gemm_bf16_workspace(M, K, x_bf16.device)
     ref = W.wref()
     check(lib().b200_nvfp4_gemm_bf16(_ptr(y), C.byref(ref), _ptr(x_bf16), M, W.N, K, _ptr(ws), stream_ptr(stream)), 'b200_nvfp4_gemm_bf16')
+    return y
+
+
+def gemm_bf16_exact(W, x_bf16, y=None, ws=None, stream=None):
+    """The exact wide GEMM: y[M,N] f32 = x[M,K] bf16 . W^T, weights dequantised to fp16 in the kernel."""
+    M, K = x_bf16.shape
+    assert W.K == K and x_bf16.dtype == torch.bfloat16
+    if y is None:
+        y = torch.empty((M, W.N), dtype=torch.float32, device=x_bf16.device)
+    if ws is None:
+        ws = torch.empty(lib().b200_nvfp4_gemm_bf16_exact_workspace_bytes(M, K), dtype=torch.uint8, device=x_bf16.device)
+    ref = W.wref()
+    check(lib().b200_nvfp4_gemm_bf16_exact(_ptr(y), C.byref(ref), _ptr(x_bf16), M, W.N, K, _ptr(ws), stream_ptr(stream)), 'b200_nvfp4_gemm_bf16_exact')
     return y
 
 

@@ -96,4 +96,8 @@ int quant_act_launch(int mode, const void* x, const void* x2, float limit, const
 int gemm_mxf4_table(const GxJob* table, int max_jobs, long expected_jobs, int NT, int N, int K, int R, const unsigned char* xq, size_t x_rows,
                     const unsigned char* sfb, size_t sfb_rows, cudaStream_t s);
 
+// gemm_f16w.cu: the exact wide GEMM (weights dequantised to fp16 in the kernel, tcgen05 kind::f16).
+size_t gemm_f16w_ws_bytes(int M, int K);
+int gemm_f16w_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s);
+
 }  // namespace b200

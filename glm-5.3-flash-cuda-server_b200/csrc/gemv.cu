@@ -484,7 +484,7 @@ extern "C" int b200_nvfp4_gemm(float* y, const b200_wref* W, const float* x, int
 
 extern "C" size_t b200_nvfp4_split_workspace_bytes(int M, int K) {
     if (M < 1 || K < 256) return 256;
-    return std::max((umma_presplit_bytes(M, K) + 255) / 256 * 256, gemm_mxf4_ws_bytes(M, K));
+    return std::max(std::max((umma_presplit_bytes(M, K) + 255) / 256 * 256, gemm_mxf4_ws_bytes(M, K)), M >= PREFILL_MIN_ROWS ? gemm_f16w_ws_bytes(M, K) : (size_t)0);
 }
 
 extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, int M, int N, int K,
@@ -492,8 +492,11 @@ extern "C" int b200_nvfp4_gemm_ws(float* y, const b200_wref* W, const float* x, 
     if (!W || M < 1) return B200_EINVAL;
     if (!W->packed || !ws || M < 3 || !use_umma() || force_general()) return b200_nvfp4_gemm(y, W, x, M, N, K, dtype, stream);
     if ((uintptr_t)ws & 255) return B200_EALIGN;
-    if (M >= PREFILL_MIN_ROWS && prefill_fp4_option()) {       // prefill widths: W once per 256 rows, NVFP4 activations
-        const int rc = gemm_mxf4_dense(y, W, x, 1, M, N, K, ws, stream);
+    if (M >= PREFILL_MIN_ROWS) {
+        // prefill widths: W once per call.  NVFP4 activations on the block-scaled MMA, or (option off) exact
+        // products on the f16 MMA with the weights dequantised inside the kernel
+        const int rc = prefill_fp4_option() ? gemm_mxf4_dense(y, W, x, 1, M, N, K, ws, stream)
+                                            : gemm_f16w_dense(y, W, x, 1, M, N, K, ws, stream);
         if (rc != B200_ENOTIMPL) return rc;
     }
     credit(B200_CREDIT_GEMM, (double)((M + B200_GEMV_M_MAX - 1) / B200_GEMV_M_MAX) * N * K * 0.5625);

@@ -112,7 +112,8 @@ int b200_nvfp4_selftest_bounded_wait(b200_stream stream);
  * scratch and 16 or more activation rows -- b200_nvfp4_gemm_ws with M >= 16, the MoE block with 16
  * or more tokens on a prepared layer -- run the wide tensor-core GEMM, which quantises the
  * activations to NVFP4 per token (see b200_nvfp4_gemm_bf16 for what that costs in accuracy).  With
- * 0 those calls keep fp32-activation accuracy at every M, in passes of 8 rows over the weights. */
+ * 0 those calls keep fp32-activation accuracy at every M: b200_nvfp4_gemm_ws through the exact wide GEMM
+ * (b200_nvfp4_gemm_bf16_exact), the MoE block in passes of 8 rows over the experts. */
 enum { B200_OPT_STABLE_WEIGHTS = 1, B200_OPT_PREFILL_FP4 = 2 };
 int b200_nvfp4_set_option(int option, int value);
 
@@ -178,6 +179,19 @@ int b200_nvfp4_gemv_multi_ws(const b200_gemv_job* jobs, int n, int M, int K, int
 size_t b200_nvfp4_gemm_bf16_workspace_bytes(int M, int K);
 int b200_nvfp4_gemm_bf16(float* y, const b200_wref* W, const void* x_bf16, int M, int N, int K,
                          void* ws, b200_stream stream);
+
+/* The EXACT wide GEMM: the same call with fp32-activation accuracy.  The NVFP4 weights are dequantised to
+ * fp16 inside the kernel (e2m1 * e4m3 is an fp16 number), the bf16 activations are scaled per token by a
+ * power of two into fp16, and the products run on tcgen05.mma kind::f16 with fp32 accumulation: results
+ * match the reference's fp32-activation gemm (kernels/gemv.cu:246-329) to fp32 rounding (measured
+ * rel-L2 < 1e-6), W still crosses HBM once per call, and the tensor pipe runs at the bf16 rate instead
+ * of the FP4 rate.  Same shape and alignment conditions as b200_nvfp4_gemm_bf16; ws:
+ * b200_nvfp4_gemm_bf16_exact_workspace_bytes(M, K) bytes.  b200_nvfp4_gemm_ws takes this path for
+ * M >= 16 when B200_OPT_PREFILL_FP4 is 0 (f32 rows are then rounded to fp16 once: rel-L2 about 1.4e-4).
+ * No counterpart in the reference. */
+size_t b200_nvfp4_gemm_bf16_exact_workspace_bytes(int M, int K);
+int b200_nvfp4_gemm_bf16_exact(float* y, const b200_wref* W, const void* x_bf16, int M, int N, int K,
+                               void* ws, b200_stream stream);
 
 /* Per-token activation quantiser of the wide GEMM: every row of x[M,K] (bf16 when x_is_f32 == 0, else
  * f32) is quantised with the reference's quant_block rule (tools/requant_dense_nvfp4.py:53-68) and its
