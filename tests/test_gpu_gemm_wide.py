@@ -198,7 +198,7 @@ def test_gemm_bf16_exact_vs_oracle(M, N, K):
     P.gemm_bf16_exact(P.Nvfp4Weight(*t), to_dev_bf16(bits), y)
     ref = O.gemm(O.bf16_bits_to_f32(bits), *t)
     r = O.rel_l2(y.cpu().numpy(), ref)
-    assert r <= 2e-6, r                               # two hundred times inside the 1e-3 bar: only fp32 accumulation
+    assert r <= 1e-5, r                               # a hundred times inside the 1e-3 bar: only the fp32 accumulation over K
     assert np.abs(ref).max() > 0
     assert P.device_status() == 0
 
@@ -227,5 +227,5 @@ def test_gemm_bf16_exact_full_size_vs_oracle(big, N):
     for M in (32, 128, 512):
         y = torch.full((M, N), float('nan'), device='cuda')
         P.gemm_bf16_exact(W, xd[:M].contiguous(), y)
-        assert O.rel_l2(y.cpu().numpy(), exact[:M]) <= 2e-6
+        assert O.rel_l2(y.cpu().numpy(), exact[:M]) <= 1e-5
     assert P.device_status() == 0
