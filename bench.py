@@ -254,6 +254,19 @@ def bench_gemm_wide(P, N, M, steps, warmup):
     return ms, 2.0 * M * N * K_HID, nv_bytes(N, K_HID) + M * K_HID * 2 + M * N * 4, dev
 
 
+def bench_gemm_exact(P, N, M, steps, warmup):
+    """The exact wide GEMM (b200_nvfp4_gemm_bf16_exact: weights dequantised to fp16 in the kernel, f16 MMA)."""
+    base, _ = make_weight(P, N, K_HID, 998)
+    copies = max(2, int(2.2 * L2_BYTES / nv_bytes(N, K_HID)) + 1)
+    ws_ = [base] + [clone_weight(P, base) for _ in range(copies - 1)]
+    x = torch.randn((M, K_HID), device='cuda', generator=torch.Generator(device='cuda').manual_seed(3)).to(torch.bfloat16)
+    y = torch.empty((M, N), device='cuda')
+    scratch = torch.empty(P.lib().b200_nvfp4_gemm_bf16_exact_workspace_bytes(M, K_HID), dtype=torch.uint8, device='cuda')
+    ms = time_steps([lambda W=W: P.gemm_bf16_exact(W, x, y, scratch) for W in ws_], steps, warmup)
+    exact = x.float() @ P.dequantize(base).t()
+    return ms, 2.0 * M * N * K_HID, nv_bytes(N, K_HID) + M * K_HID * 2 + M * N * 4, ((y - exact).norm() / exact.norm()).item()
+
+
 def bench_dense_mlp(P, steps, warmup):
     """The dense-layer MLP of the reference (kernels/layer.cu:235-254) at its shapes, one token: gate and up
     [12288 x 4096] as one 2-job launch, down [4096 x 12288] with the clamped SwiGLU applied as its
@@ -567,7 +580,7 @@ def main():
     ap.add_argument('--ep-tokens', default='256,2048', help='token counts of the expert-parallel workload')
     ap.add_argument('--gemm-shapes', default='12288x32,12288x128,12288x512,4096x32,4096x128,4096x512', help='NxM list of the prefill GEMM sub-workloads')
     ap.add_argument('--profile', default='', help='run ONE small workload a few times and exit (for ncu captures): siblings, gemm_NxM, quant, moe_mM, moe_prefill_mM')
-    ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,lm_head,siblings,gemm,dense_mlp,kda,moe,moe_prefill,ep,quant)')
+    ap.add_argument('--only', default='', help='comma list of sub-workloads to run (gemv,lm_head,siblings,gemm,gemm_exact,dense_mlp,kda,moe,moe_prefill,ep,quant)')
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     a.ep_tokens = [int(t) for t in str(a.ep_tokens).split(',') if t]
@@ -670,6 +683,13 @@ def main():
                     'frac_of_fp4_peak_4x_bf16': fl / (m * 1e-3) / 1e12 / fp4_peak, 'bytes_w_read_once': b,
                     'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak, 'rel_l2_vs_exact_product': dev_exact,
                     'launches_per_step': 2, 'kernels': 'k_quant_act + k_gemm_mxf4'}
+    if want('gemm_exact'):
+        for N, M in [tuple(int(v) for v in sh.split('x')) for sh in a.gemm_shapes.split(',') if sh]:
+            m, fl, b, dev_exact = bench_gemm_exact(P, N, M, max(20, sub_steps // 5), a.warmup)
+            sub['gemm_bf16_exact_%dx4096_M%d' % (N, M)] = {
+                'us': m * 1e3, 'tflops': fl / (m * 1e-3) / 1e12, 'frac_of_measured_bf16_peak': fl / (m * 1e-3) / 1e12 / 1652.6,
+                'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak, 'rel_l2_vs_exact_product': dev_exact,
+                'launches_per_step': 2, 'kernels': 'k_act_f16 + k_gemm_f16w'}
     if want('dense_mlp'):
         m, b = bench_dense_mlp(P, max(50, sub_steps // 5), a.warmup)
         sub['dense_mlp_12288_M1'] = {'us': m * 1e3, 'bytes': b, 'tbps': b / (m * 1e-3) / 1e12, 'frac_of_measured_hbm': b / (m * 1e-3) / 1e9 / peak}
@@ -738,6 +758,13 @@ def profile_mode(P, name):
         x = torch.randn((1, K_HID), device='cuda')
         for _ in range(reps):
             P.gemv_multi(Ws, x, 1)
+    elif name.startswith('gemmx_'):                   # the exact wide GEMM (f16 MMA)
+        N, M = (int(v) for v in name[6:].split('x'))
+        Ws = [make_weight(P, N, K_HID, 998 + i)[0] for i in range(reps)]
+        x = torch.randn((M, K_HID), device='cuda').to(torch.bfloat16)
+        y = torch.empty((M, N), device='cuda')
+        for W in Ws:
+            P.gemm_bf16_exact(W, x, y)
     elif name.startswith('gemm_'):
         N, M = (int(v) for v in name[5:].split('x'))
         Ws = [make_weight(P, N, K_HID, 998 + i)[0] for i in range(reps)]          # a fresh weight per launch

@@ -13,11 +13,12 @@
 //
 // One CTA of 16 warps per (128 weight rows, job of up to NT activation rows); K in super-steps of 256 (one TMA
 // box of packed weights) = two half-steps of 128 (what the fp16 operand buffers hold).
-//   warp 0      TMA: packed weights [128 B x 128 rows] (128B-swizzled) into a ring, weight-scale slabs
+//   warp 0      TMA: per super-step the packed weights [128 B x 128 rows] (128B-swizzled) and their scale bytes
+//               [16 B x 128 rows] into one slot of a ring
 //   warp 3      TMA: per half-step two boxes [128 B x NT rows] of the fp16 activations (64 k each)
 //   warps 4-11  converters: per half-step 128 rows x 128 k: cvt.rn.f16x2.e2m1x2, times the group's scale
-//               (e4m3 -> f16, exact), stored as the K-major 128B-swizzled fp16 tile the MMA reads; two
-//               operand buffers, so that converting half-step h+1 overlaps the MMAs of half-step h
+//               (e4m3 -> f16, exact), stored as the K-major 128B-swizzled fp16 tile the MMA reads; several
+//               operand buffers, so that the conversion runs ahead of the MMAs
 //   warp 1      MMA issuer: 8 tcgen05.mma.kind::f16 (K = 16 each) per half-step, tcgen05.commit frees
 //               the operand buffer, the activation slot and (every second half-step) the packed slot
 //   warp 2      TMEM allocation;  warps 12-15  epilogue: D[128 rows, NT tokens] * 2^e[token] / gs_w -> y
@@ -35,14 +36,13 @@ namespace b200 {
 constexpr int GF_THREADS = 512;
 constexpr int GF_CONV = 256;
 constexpr int GF_MAX_SUPER = 64, GF_MAX_HALF = 128;          // K <= 16384
-constexpr int GF_MAX_SLABS = 16;
-constexpr uint32_t GF_P_BYTES = 16384;                       // packed weights of a super-step: 128 rows x 128 B
+constexpr uint32_t GF_P_BYTES = 16384 + 2048;                // a super-step: packed weights 128 rows x 128 B, then their scales 128 rows x 16 B
 constexpr uint32_t GF_A16_BYTES = 32768;                     // fp16 operand of a half-step: 2 k-blocks x [128 rows x 128 B]
 
 struct GfParams {
     float* y; const float* gs_w; const float* rowscale;      // rowscale[m] = 2^e of token m (NaN for a non-finite token)
     unsigned int* status;
-    int M, N, K, n_jobs, sp, sb, nslot, sps, sc_box, sc_swz, prefetch_before_wait;
+    int M, N, K, n_jobs, sp, sb, na, prefetch_before_wait;      // ring slots: packed, activations, fp16 operand buffers
 };
 
 __device__ __forceinline__ void gf_tma_2d(uint32_t dst, const void* map, int x, int y, uint32_t bar) {
@@ -59,19 +59,17 @@ k_gemm_f16w(const __grid_constant__ GfParams p, const __grid_constant__ CUtensor
             const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s) {
     constexpr uint32_t B_BYTES = 2u * NT * 128u;             // activations of a half-step: 2 k-blocks x [NT rows x 128 B]
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t fullP[GF_MAX_SUPER], fullB[GF_MAX_HALF], a16_full[GF_MAX_HALF], done16[GF_MAX_HALF], slab_bar[GF_MAX_SLABS], done_bar;
+    __shared__ uint64_t fullP[GF_MAX_SUPER], fullB[GF_MAX_HALF], a16_full[GF_MAX_HALF], done16[GF_MAX_HALF], done_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ float sx[NT];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, nsup = K >> 8, nhalf = K >> 7;
     const int tile_n = (int)blockIdx.x / p.n_jobs, ji = (int)blockIdx.x - tile_n * p.n_jobs;
     const int rown0 = tile_n * 128, m0 = ji * NT, rows = min(NT, p.M - m0);
-    const uint32_t slab_bytes = 128u * (uint32_t)p.sc_box;
 
     unsigned char* ringP = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
-    unsigned char* a16 = ringP + (size_t)p.sp * GF_P_BYTES;          // two operand buffers
-    unsigned char* ringB = a16 + 2 * GF_A16_BYTES;
-    unsigned char* scl = ringB + (size_t)p.sb * B_BYTES;             // slab ring [128 x sc_box]
+    unsigned char* a16 = ringP + (size_t)p.sp * GF_P_BYTES;          // na operand buffers
+    unsigned char* ringB = a16 + (size_t)p.na * GF_A16_BYTES;
 
     pdl_launch_dependents();
     for (int i = tid; i < nsup; i += GF_THREADS) mbar_init(smem_u32(&fullP[i]), 1);
@@ -80,7 +78,6 @@ k_gemm_f16w(const __grid_constant__ GfParams p, const __grid_constant__ CUtensor
         mbar_init(smem_u32(&a16_full[i]), GF_CONV / 32);
         mbar_init(smem_u32(&done16[i]), 1);
     }
-    if (tid < GF_MAX_SLABS) mbar_init(smem_u32(&slab_bar[tid]), 1);
     if (tid == 0) mbar_init(smem_u32(&done_bar), 1);
     mbar_fence_init();
     if (warp == 2) {
@@ -91,26 +88,22 @@ k_gemm_f16w(const __grid_constant__ GfParams p, const __grid_constant__ CUtensor
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_s;
-    const int sps = p.sps;
 
     if (warp == 0) {
-        // ---- packed weights and scale slabs: lane l issues super-steps l, l + 32, .. ----
+        // ---- packed weights and their scales: lane l issues super-steps l, l + 32, .. ----
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
             asm volatile("prefetch.tensormap [%0];" :: "l"(&map_s) : "memory");
         }
         if (!p.prefetch_before_wait) pdl_wait();
         for (int g = lane; g < nsup; g += 32) {
-            if ((p.sc_swz ? (g & 7) : g) == 0) {
-                const int j = p.sc_swz ? (g >> 3) : 0;
-                // the slot is free once the MMAs of the last half-step that read the slab before it are done
-                if (j >= p.nslot) mbar_wait_spin(smem_u32(&done16[2 * ((j - p.nslot + 1) * sps) - 1]), 0, p.status, 20);
-                mbar_expect_tx(smem_u32(&slab_bar[j]), slab_bytes);
-                gf_tma_2d(smem_u32(scl) + (uint32_t)(j % p.nslot) * slab_bytes, &map_s, j * p.sc_box, rown0, smem_u32(&slab_bar[j]));
-            }
-            if (g >= p.sp) mbar_wait_spin(smem_u32(&done16[2 * (g - p.sp) + 1]), 0, p.status, 21);
-            mbar_expect_tx(smem_u32(&fullP[g]), GF_P_BYTES);
-            gf_tma_2d(smem_u32(ringP) + (uint32_t)(g % p.sp) * GF_P_BYTES, &map_w, g * 128, rown0, smem_u32(&fullP[g]));
+            // the slot is free once the operand of the second half-step of the super-step that held it has been
+            // converted (a16_full), not only multiplied: the MMAs never read the packed bytes
+            if (g >= p.sp) mbar_wait_spin(smem_u32(&a16_full[2 * (g - p.sp) + 1]), 0, p.status, 21);
+            const uint32_t bar = smem_u32(&fullP[g]), dst = smem_u32(ringP) + (uint32_t)(g % p.sp) * GF_P_BYTES;
+            mbar_expect_tx(bar, GF_P_BYTES);
+            gf_tma_2d(dst, &map_w, g * 128, rown0, bar);
+            gf_tma_2d(dst + 16384, &map_s, g * 16, rown0, bar);                  // the super-step's 16 scale bytes of every row
         }
         __syncwarp();
     } else if (warp == 3) {
@@ -137,7 +130,7 @@ k_gemm_f16w(const __grid_constant__ GfParams p, const __grid_constant__ CUtensor
             mbar_wait_spin(smem_u32(&fullB[h]), 0, p.status, 25);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const uint64_t oA = (uint64_t)(((uint32_t)(h & 1) * GF_A16_BYTES) >> 4), oB = (uint64_t)(((uint32_t)(h % p.sb) * B_BYTES) >> 4);
+                const uint64_t oA = (uint64_t)(((uint32_t)(h % p.na) * GF_A16_BYTES) >> 4), oB = (uint64_t)(((uint32_t)(h % p.sb) * B_BYTES) >> 4);
                 #pragma unroll
                 for (int kb = 0; kb < 2; ++kb) {
                     #pragma unroll
@@ -157,24 +150,20 @@ k_gemm_f16w(const __grid_constant__ GfParams p, const __grid_constant__ CUtensor
         __syncwarp();
     } else if (warp >= 4 && warp < 12) {
         // ---- converters: thread -> (weight row r, k-block kb of the half-step) ----
-        const int t = tid - 128, r = t >> 1, kb = t & 1;
+        const int t = tid - 128, r = t & 127, kb = t >> 7;      // a quarter-warp = 8 consecutive rows: conflict-free swizzled accesses
         for (int h = 0; h < nhalf; ++h) {
             const int g = h >> 1, half = h & 1;
-            const int j = p.sc_swz ? (g >> 3) : 0, is = p.sc_swz ? (g & 7) : g;
-            mbar_wait_spin(smem_u32(&slab_bar[j]), 0, p.status, 26);
             mbar_wait_spin(smem_u32(&fullP[g]), 0, p.status, 27);
-            if (h >= 2) mbar_wait_spin(smem_u32(&done16[h - 2]), 0, p.status, 28);      // the operand buffer is free again
+            if (h >= p.na) mbar_wait_spin(smem_u32(&done16[h - p.na]), 0, p.status, 28);      // the operand buffer is free again
             const unsigned char* pk = ringP + (size_t)(g % p.sp) * GF_P_BYTES + (size_t)r * 128;
             const int j0 = half * 4 + kb * 2;
             const uint4 w0 = *reinterpret_cast<const uint4*>(pk + (((j0) ^ (r & 7)) << 4));
             const uint4 w1 = *reinterpret_cast<const uint4*>(pk + (((j0 + 1) ^ (r & 7)) << 4));
-            const unsigned char* sl = scl + (size_t)(j % p.nslot) * slab_bytes;
-            const uint32_t soff = p.sc_swz ? ((uint32_t)r * 128u + (uint32_t)((is ^ (r & 7)) << 4)) : ((uint32_t)r * (uint32_t)p.sc_box + (uint32_t)is * 16u);
-            const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(sl + soff + half * 8 + kb * 4);      // four group scales
+            const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(ringP + (size_t)(g % p.sp) * GF_P_BYTES + 16384 + r * 16 + half * 8 + kb * 4);      // four group scales
             const uint32_t s01 = e4m3x2_to_h2((uint16_t)(sc4 & 0xffffu)), s23 = e4m3x2_to_h2((uint16_t)(sc4 >> 16));
             const uint32_t sc[4] = {__byte_perm(s01, s01, 0x1010), __byte_perm(s01, s01, 0x3232), __byte_perm(s23, s23, 0x1010), __byte_perm(s23, s23, 0x3232)};
             const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-            unsigned char* dst = a16 + (size_t)(h & 1) * GF_A16_BYTES + (size_t)kb * 16384 + (size_t)r * 128;
+            unsigned char* dst = a16 + (size_t)(h % p.na) * GF_A16_BYTES + (size_t)kb * 16384 + (size_t)r * 128;
             #pragma unroll
             for (int q = 0; q < 8; ++q) {            // word q: weights 8q .. 8q+7 of the k-block, group q / 2
                 uint32_t hh[4];
@@ -274,18 +263,16 @@ static int gf_launch(GfParams& p, const CUtensorMap& mx, const CUtensorMap& mw, 
     }
     const size_t static_smem = (size_t)ac[1] - 1, room = (size_t)ac[0] - static_smem - 2048;
     const int nsup = p.K / 256, nhalf = p.K / 128;
-    p.sps = p.sc_swz ? 8 : nsup;
-    const int slabs = nsup / p.sps;
-    if (slabs > GF_MAX_SLABS) return B200_ENOTIMPL;
-    p.nslot = std::min(slabs, 2);
-    const size_t b_slot = 2 * (size_t)NT * 128, fixed = 2 * (size_t)GF_A16_BYTES + (size_t)p.nslot * 128 * p.sc_box;
-    // split the rest between the packed ring (HBM latency) and the activation ring (L2 latency)
-    p.sb = std::min(nhalf, 4);
-    while (p.sb > 2 && fixed + (size_t)p.sb * b_slot + 2 * (size_t)GF_P_BYTES > room) --p.sb;
-    if (fixed + (size_t)p.sb * b_slot + 2 * (size_t)GF_P_BYTES > room) return B200_ENOTIMPL;
-    p.sp = (int)std::min<size_t>((room - fixed - (size_t)p.sb * b_slot) / GF_P_BYTES, (size_t)std::min(nsup, 6));
-    if (p.sp < 1) return B200_ENOTIMPL;
-    const size_t smem = (size_t)p.sp * GF_P_BYTES + fixed + (size_t)p.sb * b_slot + 1024;
+    const size_t b_slot = 2 * (size_t)NT * 128;
+    // Shared memory: two fp16 operand buffers and three packed slots, the rest for the activation ring
+    // (measured: ring depths beyond these change nothing -- the kernel is bound by the conversion).
+    p.na = 2; p.sp = std::min(nsup, 3); p.sb = std::min(nhalf, 8);
+    auto need = [&] { return (size_t)p.na * GF_A16_BYTES + (size_t)p.sb * b_slot + (size_t)p.sp * GF_P_BYTES; };
+    while (need() > room && p.sb > 2) --p.sb;
+    while (need() > room && p.sp > 2) --p.sp;
+    if (need() > room) return B200_ENOTIMPL;
+    p.na = std::min(p.na, nhalf);
+    const size_t smem = need() + 1024;
     if (!ready[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ac[0] - static_smem)) != cudaSuccess)
             return launch_failed("gemm_f16w: cudaFuncSetAttribute");
@@ -304,19 +291,20 @@ static int gf_launch(GfParams& p, const CUtensorMap& mx, const CUtensorMap& mw, 
 // y[M, N] = x[M, K] . W^T with exact products.  x_kind 0: bf16, 1: f32.  ws: gemm_f16w_ws_bytes(M, K).
 int gemm_f16w_dense(float* y, const b200_wref* W, const void* x, int x_kind, int M, int N, int K, void* ws, cudaStream_t s) {
     if (!y || !W || !W->packed || !W->scale || !W->gscale || !x || !ws || M < 1 || N < 1) return B200_EINVAL;
-    int box = 0, swz = 0;
-    if ((K & 255) || K < 256 || K > 16384 || !scale_box(K, &box, &swz) || !tmap_available()) return B200_ENOTIMPL;
+    if ((K & 255) || K < 256 || K > 16384 || !tmap_available()) return B200_ENOTIMPL;
     if (((uintptr_t)W->packed & 15) || ((uintptr_t)W->scale & 15) || ((uintptr_t)x & 15) || ((uintptr_t)ws & 255)) return B200_ENOTIMPL;
     __half* xh = static_cast<__half*>(ws);
     float* rowscale = reinterpret_cast<float*>(static_cast<char*>(ws) + up256((size_t)M * K * 2));
+    // The conversion of a 128-row weight tile costs a CTA 9-12 us of the SFU pipe (cvt.e2m1x2 runs there), so it
+    // is shared by as many tokens as one accumulator holds; 64-token tiles were measured slower from 65 rows on.
     const int NT = M <= 64 ? 64 : 128, n_jobs = (M + NT - 1) / NT, tiles_n = (N + 127) / 128;
     GfParams p{};
     p.y = y; p.gs_w = W->gscale; p.rowscale = rowscale; p.status = device_status_ptr();
     if (!p.status) return B200_ENOTIMPL;
-    p.M = M; p.N = N; p.K = K; p.n_jobs = n_jobs; p.sc_box = box; p.sc_swz = swz; p.prefetch_before_wait = stable_weights_option();
+    p.M = M; p.N = N; p.K = K; p.n_jobs = n_jobs; p.prefetch_before_wait = stable_weights_option();
     CUtensorMap mx, mw, ms;
     if (!tmap_u8_2d(&mw, W->packed, (size_t)N, (size_t)K / 2, 128, 128, true, true) ||
-        !tmap_u8_2d(&ms, W->scale, (size_t)N, (size_t)K / 16, box, 128, swz != 0, true) ||
+        !tmap_u8_2d(&ms, W->scale, (size_t)N, (size_t)K / 16, 16, 128, false, true) ||
         !tmap_u8_2d(&mx, xh, (size_t)M, (size_t)K * 2, 128, NT, true, true)) return B200_ENOTIMPL;
     credit(B200_CREDIT_GEMM, (double)n_jobs * N * K * 0.5625);
     {
