@@ -41,6 +41,12 @@
 // parked at the closing barrier is scheduled rarely: measured 20 % slower).  Before it exits a CTA
 // waits for the last tcgen05.commit arrival of every stage: an arrival still in flight would land
 // in the shared memory of the next CTA on that SM.
+// Decode kernel with RESIDENT scales (RES; one row, one tile, K <= 7424): TMEM has room for the scales of every
+// step at once, so the MMA warps (idle until the activations are split) move them all as soon as the slabs have
+// landed -- with weights declared stable that is before the dependency wait -- and the shared memory of the
+// slabs then serves as further ring stages.  For the
+// decode shapes (K = 4096, R <= 96) the ring then holds the CTA's whole tile: every weight byte is requested
+// before the wait, and after the activation split the MMAs run at issue speed.
 // Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast.
 #include "b200_internal.h"
 #include "nvfp4_decode.cuh"
@@ -62,8 +68,10 @@ constexpr int UM_NB = 8;                           // MMA N = digits per activat
 constexpr int UM_MAX_M = 8;                        // activation rows per job (MMA N = 8 * M <= 64)
 constexpr int UM_MAX_STAGES = 12;                  // TMEM holds one 16-column scale slot per stage
 constexpr int UM_MAX_STEPS = 64;                   // K <= 16384
-constexpr int UM_TMEM_COLS = 512;                  // D0..D3 [0,256), 64 each | unit scales [256,260) | per-stage weight scales [272, 272+16*stages)
+constexpr int UM_TMEM_COLS = 512;                  // D0..D3 [0,256), 64 each | unit scales [256,260) | weight scales from 272, 16 columns per slot
 constexpr int UM_COL_SB = 256, UM_COL_SF = 272;
+constexpr int UM_RES_ACC = 8, UM_RES_SB = 32, UM_RES_SF = 48;      // decode kernel with resident scales: D0..D3 [0,32) | unit scales [32,36) | step g's scales [48 + 16 g, ..)
+constexpr int UM_RES_STEPS = (UM_TMEM_COLS - UM_RES_SF) / 16;      // 29 steps: K <= 7424
 
 
 struct UmParams {
@@ -76,6 +84,9 @@ struct UmParams {
     int T;                                         // consecutive row tiles of one job per CTA (T * max_m <= 8, T * K/256 <= 64)
     uint32_t stage_bytes;                          // per stage: the A tile, R x 128 bytes rounded up to 1 KB
     int sc_box, sc_swz;                            // scale slab: box width in bytes (128 swizzled, or K/16 plain)
+    uint32_t bimg_off, scl_off, tsc_off;           // shared-memory offsets of the B image, of the scale slabs and (resident scales) of their transposed copy from the (1 KB aligned) ring
+    int ov_first;                                  // resident scales: stages from this one on share their bytes with the scale slabs or the transposed copy
+    int early;                                     // stages requested by the producer before it waits for the other barriers (-1: not even the slabs)
 };
 
 
@@ -209,11 +220,13 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
 
 // GEN = false: the decode hot path (one activation row, one tile per CTA, jobs in the parameters,
 // plain activations) with the general loops folded away at compile time.
-template <bool GEN>
+template <bool GEN, bool RES>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps maps) {
+    static_assert(!(GEN && RES), "resident scales are a decode-kernel mode");
+    constexpr int COL_ACC = RES ? UM_RES_ACC : 64, COL_SB = RES ? UM_RES_SB : UM_COL_SB, COL_SF = RES ? UM_RES_SF : UM_COL_SF;
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar, bi_bar;
+    __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar, bi_bar, scd_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ float gam[UM_MAX_M][UM_NB], red[UM_MAX_M][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -239,58 +252,114 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     const int nsteps = T * nst;                      // step g: tile g / nst, 256-k block g % nst
     const int M = GEN ? J.M : 1;
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);      // SWIZZLE_128B tiles need 1 KB alignment
-    unsigned char* bimg = ring + (size_t)p.stages * p.stage_bytes;          // nst tiles of max_m KB: [step][row m][digit t][128 B]
-    unsigned char* scl = bimg + (size_t)nst * p.max_m * 1024;                          // all scale rows of the CTA: per tile, slabs [R x sc_box]
+    unsigned char* bimg = ring + p.bimg_off;        // nst tiles of max_m KB: [step][row m][digit t][128 B]
+    unsigned char* scl = ring + p.scl_off;          // all scale rows of the CTA: per tile, slabs [R x sc_box]
 
     pdl_launch_dependents();
-    if (warp >= UM_LOAD_WARPS + UM_MMA_WARPS) {      // barrier init spread over the worker threads
-        const int i = tid - UM_LOADERS - 32 * UM_MMA_WARPS;
-        if (i < nsteps) mbar_init(smem_u32(&full_bar[i]), 1);
-        else if (i >= 64 && i < 64 + nsteps) mbar_init(smem_u32(&sf_bar[i - 64]), 128);
-        else if (i >= 128 && i < 128 + nsteps) mbar_init(smem_u32(&empty_bar[i - 128]), 1);
-        else if (i == 192) mbar_init(smem_u32(&done_bar), UM_MMA_WARPS);
-        else if (i == 193) mbar_init(smem_u32(&sc_bar), 1);
-        else if (i == 194) mbar_init(smem_u32(&bi_bar), 1);
+    // ---- TMA producer, part one (warp 0): with weights declared stable, the scale slabs and every stage that
+    // waits for nothing are requested before anything else happens in the CTA -- before the TMEM allocation and
+    // the CTA-wide barrier, on barriers this warp initialises itself.  Lane l issues steps l, l + 32, ...
+    const uint32_t full0 = smem_u32(&full_bar[0]), ring0 = smem_u32(ring);
+    const int n_early = p.prefetch_before_wait ? min(min(p.stages, p.ov_first), p.early) : 0;
+    const bool early_scales = p.prefetch_before_wait && p.early >= 0;
+    auto issue_scales = [&]() {
+        // All scale rows of the CTA, in slabs [R rows x sc_box bytes]: one tensor load per slab instead of one
+        // [R x 16 B] box per step (a box costs the TMA unit ~1 ns per row whatever the row's width).  128-byte
+        // slabs are stored 128B-swizzled, so that 32 lanes reading the same 16-byte column of 32 consecutive
+        // rows hit different banks.
+        const int nslab = (K >> 4) / p.sc_box;
+        const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
+        if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), slab_bytes * (uint32_t)T);
+        __syncwarp();
+        for (int q = lane; q < T * nslab; q += 32) {
+            const int t = q / nslab, sl = q - t * nslab;
+            tma_load_2d(smem_u32(scl) + (uint32_t)t * slab_bytes + (uint32_t)sl * (uint32_t)p.R * (uint32_t)p.sc_box,
+                        (const CUtensorMap*)J.ms, sl * p.sc_box, row0 + t * p.R, smem_u32(&sc_bar));
+        }
+    };
+    auto issue_stage = [&](int g) {
+        const int s = g % p.stages, t = g / nst, it = g - t * nst;
+        const uint32_t bar = full0 + g * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
+        mbar_expect_tx(bar, (uint32_t)p.R * 128u);
+        tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0 + t * p.R, bar);
+    };
+    if (warp == 0) {
+        for (int i = lane; i < nsteps; i += 32) mbar_init(full0 + i * 8, 1);
+        if (lane == 0) mbar_init(smem_u32(&sc_bar), 1);
         mbar_fence_init();
+        __syncwarp();
+        if (early_scales) {
+            issue_scales();
+            for (int g = lane; g < n_early; g += 32) issue_stage(g);
+        }
     }
-    if (warp == UM_LOAD_WARPS) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_base_s)), "r"(UM_TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    // No CTA-wide barrier in the prologue: the workers go straight to the dependency wait and the activation
+    // loads (the longest chain of the kernel); the MMA warps initialise the other barriers and allocate TMEM,
+    // and meet the producer at named barrier 3; the workers learn of all that at named barrier 2.
+    const bool mma_warp = warp >= UM_LOAD_WARPS && warp < UM_LOAD_WARPS + UM_MMA_WARPS;
+    if (mma_warp) {
+        const int i = tid - UM_LOADERS;
+        for (int k = i; k < nsteps; k += 32 * UM_MMA_WARPS) {
+            mbar_init(smem_u32(&sf_bar[k]), 128);
+            mbar_init(smem_u32(&empty_bar[k]), 1);
+        }
+        if (i == 0) mbar_init(smem_u32(&done_bar), UM_MMA_WARPS);
+        if (i == 1) mbar_init(smem_u32(&scd_bar), UM_MMA_WARPS);
+        mbar_fence_init();
+        if (warp == UM_LOAD_WARPS) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&tmem_base_s)), "r"(UM_TMEM_COLS));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+        }
+        tc_fence_before();
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_base_s;
+    // The producer waits at barrier 3 for the MMA warps' initialisations; they only arrive there (the
+    // producer has nothing they need) and meet among themselves at barrier 4 for the TMEM address.
+    if (warp == 0) named_sync(3, 32 + 32 * UM_MMA_WARPS);
+    if (mma_warp) {
+        asm volatile("bar.arrive 3, %0;" :: "r"(32 + 32 * UM_MMA_WARPS) : "memory");
+        named_sync(4, 32 * UM_MMA_WARPS);
+    }
+    uint32_t tmem = 0u, tq = 0u;                     // TMEM base; the lane quadrant this warp may access (set once the role knows the base)
+    // Weight scales, shared memory -> TMEM.  Lane l holds rows l, l+32, l+64, l+96: 16 bytes each = four
+    // k-blocks x four scales; k-block kb of row 32c + l goes to column kb*4 + c.  Within a group of four
+    // warps each warp writes its own TMEM lane quadrant (the MMA wants the 32-lane block in all four).
+    const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
+    auto load_scales = [&](int t, int it, uint4 (&v)[4]) {
+        const unsigned char* sl = scl + (uint32_t)t * slab_bytes;
+        const int valid = J.N - (row0 + t * p.R);            // rows of this tile that exist (may exceed R)
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int r = lane + 32 * c;
+            uint32_t off;
+            if (p.sc_swz) off = (uint32_t)(it >> 3) * (uint32_t)p.R * 128u + (uint32_t)r * 128u + (uint32_t)(((it & 7) ^ (r & 7)) << 4);
+            else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)it * 16u;
+            v[c] = (r < p.R && r < valid) ? *reinterpret_cast<const uint4*>(sl + off) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto store_scales = [&](uint32_t slot, const uint4 (&v)[4]) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                     :: "r"(tq + COL_SF + slot * 16u),
+                        "r"(v[0].x), "r"(v[1].x), "r"(v[2].x), "r"(v[3].x), "r"(v[0].y), "r"(v[1].y), "r"(v[2].y), "r"(v[3].y),
+                        "r"(v[0].z), "r"(v[1].z), "r"(v[2].z), "r"(v[3].z), "r"(v[0].w), "r"(v[1].w), "r"(v[2].w), "r"(v[3].w) : "memory");
+    };
 
     if (warp < UM_LOAD_WARPS) {
-        // ---- TMA producer: warp 0; lane l issues the loads of steps l, l + 32, ... ----
+        // ---- TMA producer, part two: warp 0; lane l issues the loads of steps l, l + 32, ... ----
         // One thread issuing tensor loads back to back gets one out every ~0.35 us (measured), so
         // the steps are dealt to the lanes: each lane waits for its own stage and issues on its own.
         if (warp == 0) {
-            if (lane == 0) { asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
-                             asm volatile("prefetch.tensormap [%0];" :: "l"(J.ms) : "memory"); }
-            if (!p.prefetch_before_wait) pdl_wait();
-            // All scale rows of the CTA first, in slabs [R rows x sc_box bytes]: one tensor load per
-            // slab instead of one [R x 16 B] box per step (a box costs the TMA unit ~1 ns per row
-            // whatever the row's width).  128-byte slabs are stored 128B-swizzled, so that 32 lanes
-            // reading the same 16-byte column of 32 consecutive rows hit different banks.
-            const int nslab = (K >> 4) / p.sc_box;
-            const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
-            if (lane == 0) mbar_expect_tx(smem_u32(&sc_bar), slab_bytes * (uint32_t)T);
-            __syncwarp();
-            for (int q = lane; q < T * nslab; q += 32) {
-                const int t = q / nslab, sl = q - t * nslab;
-                tma_load_2d(smem_u32(scl) + (uint32_t)t * slab_bytes + (uint32_t)sl * (uint32_t)p.R * (uint32_t)p.sc_box,
-                            (const CUtensorMap*)J.ms, sl * p.sc_box, row0 + t * p.R, smem_u32(&sc_bar));
+            const uint32_t empty0 = smem_u32(&empty_bar[0]);
+            if (!early_scales) {
+                if (lane == 0) { asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
+                                 asm volatile("prefetch.tensormap [%0];" :: "l"(J.ms) : "memory"); }
+                if (!p.prefetch_before_wait) pdl_wait();
+                issue_scales();
             }
-            const uint32_t bytes = (uint32_t)p.R * 128u;
-            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]), ring0 = smem_u32(ring);
             for (int g = lane; g < nsteps; g += 32) {
-                const int s = g % p.stages, t = g / nst, it = g - t * nst;
+                if (g < n_early) continue;
                 if (g >= p.stages) UM_WAIT(empty0 + (g - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
-                const uint32_t bar = full0 + g * 8, dst = ring0 + (uint32_t)s * p.stage_bytes;
-                mbar_expect_tx(bar, bytes);
-                tma_load_2d(dst, (const CUtensorMap*)J.mw, it * 128, row0 + t * p.R, bar);
+                else if (RES && g % p.stages >= p.ov_first) UM_WAIT(smem_u32(&scd_bar), 0, p.status, 8);   // the slabs under this stage are in TMEM
+                issue_stage(g);
             }
             __syncwarp();
             // Tail: the tcgen05.commit arrivals on empty_bar are asynchronous.  Wait for the last one
@@ -304,7 +373,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // L2 prefetch of the steps the ring cannot take at once (legal before the upstream kernel
             // has finished: L2 is the point of coherence).  Only on the single-tile path: a prefetch
             // costs the TMA unit as much as a load, and a multi-tile CTA would queue dozens of them.
-            for (int g = p.stages + lane; g < nsteps; g += 32) {
+            for (int g = (RES ? min(p.stages, p.ov_first) : p.stages) + lane; g < nsteps; g += 32) {
                 const int t = g / nst, it = g - t * nst;
                 asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
                              :: "l"(J.mw), "r"(it * 128), "r"(row0 + t * p.R) : "memory");
@@ -312,24 +381,75 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         }
     } else if (warp < UM_LOAD_WARPS + UM_MMA_WARPS) {
         // ---- MMA issuers: warp w takes the steps g with g % 4 == w ----
-        named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // B image, unit scales and gam[] are ready
+        tc_fence_after();
+        tmem = tmem_base_s;
+        tq = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        {
+            // unit block scales of the activation digits (e4m3 1.0), once: each warp its own lane quadrant
+            const uint32_t one = 0x38383838u;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" :: "r"(tq + COL_SB), "r"(one) : "memory");
+        }
+        if (RES) {
+            // Resident scales: every step has its own TMEM slot, and these four warps (one per lane quadrant)
+            // have nothing else to do until the activations are split: they move all the scales, needing
+            // only the slabs.  After that the slabs' shared memory belongs to the ring (scd_bar).
+            UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
+            // Warp w takes its own MMA steps g = w, w + 4, ...  A step's scales are [R rows][4 k-blocks x 4 B] in
+            // the slab; the tensor core's copy (tcgen05.cp 32x128b.warpx4) wants, per k-block, 32 rows of 16 B
+            // where row l holds the 4-byte scales of weight rows l, l+32, l+64, l+96: it writes them to TMEM
+            // lane l, columns 0..3, in all four lane quadrants -- the layout the block-scaled MMA reads.  Lane
+            // l transposes its 4 x 4 words in registers; the copies are issued by the lane that issues the
+            // step's MMAs later (same thread: they execute in order), and a commit tells the producer when
+            // the shared memory under them is free.
+            unsigned char* tsc = ring + p.tsc_off;         // [step][k-block][32 rows][16 B]
+            const int me = warp - UM_LOAD_WARPS;
+            for (int g = me; g < nsteps; g += UM_MMA_WARPS) {
+                uint4 v[4];
+                load_scales(0, g, v);
+                uint4* o = reinterpret_cast<uint4*>(tsc + (size_t)g * 2048 + (size_t)lane * 16);
+                o[0] = make_uint4(v[0].x, v[1].x, v[2].x, v[3].x);
+                o[32] = make_uint4(v[0].y, v[1].y, v[2].y, v[3].y);
+                o[64] = make_uint4(v[0].z, v[1].z, v[2].z, v[3].z);
+                o[96] = make_uint4(v[0].w, v[1].w, v[2].w, v[3].w);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                for (int g = me; g < nsteps; g += UM_MMA_WARPS) {
+                    #pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        // 32 rows x 16 B, contiguous: four 8-row core matrices 128 B apart, no swizzle
+                        const uint64_t sd = umma_desc(smem_u32(tsc) + (uint32_t)g * 2048u + (uint32_t)kb * 512u, 128, 0) | ((uint64_t)(128 >> 4) << 16);
+                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;"
+                                     :: "r"(tmem + COL_SF + (uint32_t)g * 16u + (uint32_t)kb * 4u), "l"(sd) : "memory");
+                    }
+                }
+                tc_commit(smem_u32(&scd_bar));
+            }
+            __syncwarp();
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        if (RES && warp - UM_LOAD_WARPS < nsteps)        // this warp's first step: its weights are awaited now rather than after the barrier
+            UM_WAIT(full0 + (warp - UM_LOAD_WARPS) * 8, 0, p.status, 3);
+        const int me = warp - UM_LOAD_WARPS;
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)M << 17) | ((128u >> 4) << 24);     // N = 8 M
+        const uint64_t dA0 = umma_desc(smem_u32(ring), 1024, 2), dB0 = umma_desc(smem_u32(bimg), 1024, 2);
+        const uint32_t tSB = tmem + COL_SB;
+        const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+        named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // B image, unit and weight scales and gam[] are ready
         tc_fence_after();
         {
-            const int me = warp - UM_LOAD_WARPS;
-            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)M << 17) | ((128u >> 4) << 24);     // N = 8 M
-            const uint64_t dA0 = umma_desc(smem_u32(ring), 1024, 2), dB0 = umma_desc(smem_u32(bimg), 1024, 2);
-            const uint32_t tSB = tmem + UM_COL_SB;
-            const uint32_t sf0 = smem_u32(&sf_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             int s = me % p.stages;
             int t = me / nst, it = me - t * nst;                       // tile and k-block of step g, kept without divisions
             for (int g = me; g < nsteps; g += UM_MMA_WARPS) {          // whole warp waits, lane 0 issues
-                const uint32_t tsf = tmem + UM_COL_SF + (uint32_t)s * 16u;
+                const uint32_t tsf = tmem + COL_SF + (uint32_t)(RES ? g : s) * 16u;
                 // accumulator it % 4 of tile t: fixed by the k-block alone, so that the summation order of a
                 // row does not depend on which tile of the CTA it is in (or on how many tiles a CTA takes)
-                const uint32_t tD = tmem + (uint32_t)((it & 3) * 64 + t * 8 * M);
+                const uint32_t tD = tmem + (uint32_t)((it & 3) * COL_ACC + t * 8 * M);
                 const uint64_t dA = dA0 + (((uint32_t)s * p.stage_bytes) >> 4), dB = dB0 + (uint32_t)(it * p.max_m) * 64u;
                 const uint32_t acc0 = it >= 4;                          // the first k-block of an accumulator starts it
-                UM_WAIT(sf0 + g * 8, 0, p.status, 3);
+                UM_WAIT((RES ? full0 : sf0) + g * 8, 0, p.status, 3);      // resident scales: only the step's weights are awaited
                 tc_fence_after();
                 if (lane == 0) {
                     #pragma unroll
@@ -351,21 +471,13 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     } else {
         // ---- workers: activation split, then per-step scale copies; the first four warps also the epilogue ----
         const int t4 = tid - UM_LOADERS - 32 * UM_MMA_WARPS;      // 0..255
-        const int q4 = warp & 3;                         // TMEM lane quadrant this warp may access
-        const uint32_t tq = tmem + ((uint32_t)(q4 * 32) << 16);
-        if (t4 < 128) {
-            // unit block scales of the activation digits (e4m3 1.0), once
-            const uint32_t one = 0x38383838u;
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" :: "r"(tq + UM_COL_SB), "r"(one) : "memory");
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        }
-        if (!p.prefetch_before_wait) pdl_wait();
-        const float gsv = J.gs[0];                       // weight data: with stable weights it may be read early
+        const int q4 = warp & 3;
         pdl_wait();
+        const float gsv = J.gs[0];
         if (GEN && J.bimg) {
             // The B image was split once for all CTAs of the job by k_split_rows: copy it in.
             const uint32_t total = (uint32_t)nst * (uint32_t)p.max_m * 1024u;
-            if (t4 == 0) mbar_expect_tx(smem_u32(&bi_bar), total);
+            if (t4 == 0) { mbar_init(smem_u32(&bi_bar), 1); mbar_fence_init(); mbar_expect_tx(smem_u32(&bi_bar), total); }
             named_sync(1, UM_WORKERS);
             for (uint32_t o = (uint32_t)t4 * 16384u; o < total; o += UM_WORKERS * 16384u)
                 bulk_g2s(smem_u32(bimg) + o, J.bimg + o, min(16384u, total - o), smem_u32(&bi_bar));
@@ -377,42 +489,30 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         fence_async_smem();
         tc_fence_before();
         named_sync(2, 32 * UM_MMA_WARPS + UM_WORKERS);   // with the MMA warps
-        {
-            // Weight scales: the first four worker warps take the even steps, the other four the odd
-            // ones; within a group each warp writes its own TMEM lane quadrant (the MMA wants the
-            // 32-lane block in all four).  Lane l holds rows l, l+32, l+64, l+96: 16 bytes each =
-            // four k-blocks x four scales; k-block kb of row 32c + l goes to column kb*4 + c.
+        tc_fence_after();
+        tmem = tmem_base_s;
+        tq = tmem + ((uint32_t)(q4 * 32) << 16);
+        if (!RES) {
+            // The first four worker warps take the even steps, the other four the odd ones; a step's scales
+            // go to the TMEM slot of its stage.
             const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
             const int grp = t4 >> 7;
             int s = grp % p.stages;
             UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
             // Software-pipelined: the next step's scale bytes are read from shared memory while this
             // step's tcgen05.st is in flight.
-            const uint32_t slab_bytes = (uint32_t)p.R * (uint32_t)(K >> 4);     // one tile's scale rows
             int rt = grp / nst, rit = grp - rt * nst;                  // tile and k-block of the next step to read
             auto read_scales = [&](int g, uint4 (&v)[4]) {
                 // full[g] also says that the MMAs that last read this stage's scale slot are done
                 UM_WAIT(full0 + g * 8, 0, p.status, 2);
                 const int t = rt, it = rit;
                 rit += 2; while (rit >= nst) { rit -= nst; ++rt; }
-                const unsigned char* sl = scl + (uint32_t)t * slab_bytes;
-                const int valid = J.N - (row0 + t * p.R);            // rows of this tile that exist (may exceed R)
-                #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int r = lane + 32 * c;
-                    uint32_t off;
-                    if (p.sc_swz) off = (uint32_t)(it >> 3) * (uint32_t)p.R * 128u + (uint32_t)r * 128u + (uint32_t)(((it & 7) ^ (r & 7)) << 4);
-                    else off = (uint32_t)r * (uint32_t)p.sc_box + (uint32_t)it * 16u;
-                    v[c] = (r < p.R && r < valid) ? *reinterpret_cast<const uint4*>(sl + off) : make_uint4(0u, 0u, 0u, 0u);
-                }
+                load_scales(t, it, v);
             };
             uint4 v[4], vn[4];
             if (grp < nsteps) read_scales(grp, v);
             for (int g = grp; g < nsteps; g += 2) {
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                             :: "r"(tq + UM_COL_SF + (uint32_t)s * 16u),
-                                "r"(v[0].x), "r"(v[1].x), "r"(v[2].x), "r"(v[3].x), "r"(v[0].y), "r"(v[1].y), "r"(v[2].y), "r"(v[3].y),
-                                "r"(v[0].z), "r"(v[1].z), "r"(v[2].z), "r"(v[3].z), "r"(v[0].w), "r"(v[1].w), "r"(v[2].w), "r"(v[3].w) : "memory");
+                store_scales((uint32_t)s, v);
                 if (g + 2 < nsteps) read_scales(g + 2, vn);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
@@ -436,7 +536,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                     for (int w = 0; w < 4; ++w)
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                                      : "=r"(d[w][0]), "=r"(d[w][1]), "=r"(d[w][2]), "=r"(d[w][3]), "=r"(d[w][4]), "=r"(d[w][5]), "=r"(d[w][6]), "=r"(d[w][7])
-                                     : "r"(tq + (uint32_t)(w * 64 + t * 8 * M + m * 8)));
+                                     : "r"(tq + (uint32_t)(w * COL_ACC + t * 8 * M + m * 8)));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (r < p.R && row < J.N) {
                         float acc = 0.f;
@@ -589,12 +689,14 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     // allocation for the last stage as well.
     if (p.stage_bytes + fixed < 16384) fixed = 16384 - p.stage_bytes;
     const bool gen = p.table != nullptr || p.max_m != 1 || p.T != 1;
-    auto kern = gen ? k_gemv_umma<true> : k_gemv_umma<false>;
+    const bool res = !gen && nst <= UM_RES_STEPS;
+    const int var = gen ? 0 : res ? 2 : 1;
+    auto kern = gen ? k_gemv_umma<true, false> : res ? k_gemv_umma<false, true> : k_gemv_umma<false, false>;
     // static shared memory of the kernel and the device's opt-in limit: asked once per device and variant
-    static int attr_cache[64][2][2] = {};            // [device][variant] = {optin, static bytes + 1}
+    static int attr_cache[64][3][2] = {};            // [device][variant] = {optin, static bytes + 1}
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return launch_failed("gemv_umma: cudaGetDevice");
-    int* ac = attr_cache[dev >= 0 && dev < 64 ? dev : 0][gen];
+    int* ac = attr_cache[dev >= 0 && dev < 64 ? dev : 0][var];
     if (!ac[1]) {
         cudaFuncAttributes fa;
         int oi = 0;
@@ -607,21 +709,51 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     const size_t room = (size_t)optin - static_smem - 2048;    // 1 KB alignment slack + 1 KB system reserve
     if (fixed + 2 * (size_t)p.stage_bytes > room) return B200_ENOTIMPL;
     const int nsteps = p.T * nst;
-    p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nsteps), (room - fixed) / p.stage_bytes);
-    // The scale warps look two steps ahead before they release a step: with a ring of two that
-    // would wait for itself.
-    if (p.stages < 3 && p.stages < nsteps) return B200_ENOTIMPL;
+    size_t total;                                    // dynamic shared memory from the aligned ring base
+    if (res) {
+        // Ring | transposed scales | slabs | B image when everything fits; otherwise the transposed scales and
+        // the slabs lie under the last stages of the ring (which wait until the scales are in TMEM), so that the
+        // ring is as deep as the SM allows.
+        const size_t bimg = (size_t)nst * 1024, sc = ((size_t)R * (K / 16) + 1023) & ~(size_t)1023, tsc = (size_t)nsteps * 2048;
+        if ((size_t)nsteps * p.stage_bytes + tsc + sc + bimg <= room) {
+            p.stages = nsteps; p.tsc_off = (uint32_t)nsteps * p.stage_bytes; p.ov_first = nsteps;
+            p.scl_off = p.tsc_off + (uint32_t)tsc;
+            p.bimg_off = p.scl_off + (uint32_t)sc;
+        } else {
+            p.stages = (int)std::min<size_t>(nsteps, (room - bimg) / p.stage_bytes);
+            const size_t ring = std::max((size_t)p.stages * p.stage_bytes, tsc + sc);
+            p.scl_off = (uint32_t)(ring - sc); p.tsc_off = p.scl_off - (uint32_t)tsc;
+            p.ov_first = (int)(p.tsc_off / p.stage_bytes);
+            p.bimg_off = (uint32_t)ring;
+        }
+        total = std::max((size_t)p.bimg_off + bimg, (size_t)(p.stages - 1) * p.stage_bytes + 16384);
+        if (total > room || (p.stages < 3 && p.stages < nsteps)) return B200_ENOTIMPL;
+    } else {
+        p.stages = (int)std::min<size_t>(std::min(UM_MAX_STAGES, nsteps), (room - fixed) / p.stage_bytes);
+        // The scale warps look two steps ahead before they release a step: with a ring of two that
+        // would wait for itself.
+        if (p.stages < 3 && p.stages < nsteps) return B200_ENOTIMPL;
+        p.bimg_off = (uint32_t)p.stages * p.stage_bytes;
+        p.scl_off = p.bimg_off + (uint32_t)nst * (uint32_t)M * 1024u;
+        p.ov_first = p.stages;
+        total = (size_t)p.stages * p.stage_bytes + fixed;
+    }
     p.status = device_status_ptr();
     if (!p.status) return B200_ENOTIMPL;
     p.prefetch_before_wait = stable_weights_option();
+    // Measured on the decode shapes (six siblings, K = 4096, 16 stages resident): 4 stages at once 7.1-7.3 us per
+    // launch, 2: 7.5, 0: 7.7, 8: 7.9, all 16: 8.1-8.4.  A flood of requests from every SM at once delays what
+    // each SM needs first (its scale slabs, the activation row); pacing later requests by earlier arrivals was
+    // slower still (a window of 4 stages: 8.2, of 6: 7.5).
+    p.early = 4;
     if (p.dry_run) return B200_OK;
-    const size_t smem = (size_t)p.stages * p.stage_bytes + fixed + 1024;
-    static bool ready_all[64][2] = {};               // the attribute is per device
+    const size_t smem = total + 1024;
+    static bool ready_all[64][3] = {};               // the attribute is per device
     bool* ready = ready_all[dev >= 0 && dev < 64 ? dev : 0];
-    if (!ready[gen]) {
+    if (!ready[var]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - static_smem)) != cudaSuccess)
             return launch_failed("gemv_umma: cudaFuncSetAttribute");
-        ready[gen] = true;
+        ready[var] = true;
     }
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(tasks); lc.blockDim = dim3(UM_THREADS); lc.dynamicSmemBytes = smem; lc.stream = s;
