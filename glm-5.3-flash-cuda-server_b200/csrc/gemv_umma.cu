@@ -401,6 +401,22 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 mbar_wait(empty0 + g * 8, 0, p.status, 5);
             __syncwarp();
         }
+        else if (warp == 1 && !p.prefetch_before_wait && !(GEN && p.table) && J.pfw) {
+            // Weights not declared stable: nothing of them may be copied into shared memory before the dependency
+            // wait, but the L2 is the point of coherence, so the CTA's rows (contiguous in memory) can be asked into
+            // the L2 right away, 16 KB per instruction, and the loads after the wait find them there.
+            const int rows = min(p.R * T, J.N - row0);
+            auto prefetch = [&](const unsigned char* base, uint32_t bytes) {
+                for (uint32_t o = (uint32_t)lane * 16384u; o < bytes; o += 32u * 16384u) {
+                    const uint32_t n = min(16384u, bytes - o) & ~15u;
+                    if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + o), "r"(n) : "memory");
+                }
+            };
+            if (rows > 0) {
+                prefetch(J.pfw + (size_t)row0 * (K >> 1), (uint32_t)rows * (uint32_t)(K >> 1));
+                prefetch(J.pfs + (size_t)row0 * (K >> 4), (uint32_t)rows * (uint32_t)(K >> 4));
+            }
+        }
         else if (warp == 1 && !GEN) {
             // L2 prefetch of the steps the ring cannot take at once (legal before the upstream kernel
             // has finished: L2 is the point of coherence).  Only on the single-tile path: a prefetch
@@ -746,7 +762,8 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
     for (int i = 0; i < g.n_jobs; ++i) {
         p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr,
                        pre ? pre->img + (size_t)pre->chunk * pre->chunk_bytes : nullptr,
-                       pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0};
+                       pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0,
+                       static_cast<const unsigned char*>(g.j[i].P), static_cast<const unsigned char*>(g.j[i].S)};
         tasks += ((g.j[i].N + R - 1) / R + p.T - 1) / p.T;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;

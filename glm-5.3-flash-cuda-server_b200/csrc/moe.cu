@@ -117,6 +117,19 @@ k_router_fused(float* __restrict__ logits, const __nv_bfloat16* __restrict__ W, 
     #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m] = 0.f;
     pdl_launch_dependents();
+    if (plan.j1 && plan.shared && threadIdx.x < 6) {
+        // The shared expert runs for every token: its three matrices are asked into the L2 now, a slice per CTA,
+        // while memory is otherwise idle (the L2 is the point of coherence: legal before the dependency wait).
+        const b200_nvfp4_mat mt = plan.shared[threadIdx.x >> 1];
+        const bool sc = threadIdx.x & 1;
+        const size_t total = (size_t)plan.H * plan.I / (sc ? 16 : 2);
+        const size_t per = ((total + E - 1) / E + 15) & ~(size_t)15, lo = min(per * n, total), hi = min(lo + per, total);
+        const unsigned char* base = static_cast<const unsigned char*>(sc ? (const void*)mt.scale : (const void*)mt.packed);
+        for (size_t o = lo; o < hi; o += 16384) {
+            const uint32_t nb = (uint32_t)min((size_t)16384, hi - o) & ~15u;
+            if (nb) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + o), "r"(nb) : "memory");
+        }
+    }
     uint4 pre[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
     if (early) {                                   // router weights declared stable: requested before the dependency wait
         #pragma unroll
