@@ -54,18 +54,6 @@ int nvfp4_math_mode();
 // gemv_tma.cu: single-row (M = 1) bulk-copy pipelined kernel; returns B200_ENOTIMPL when the
 // shapes / alignments it needs do not hold, and the caller then uses the general kernel.
 int nvfp4_multi_tma(const GemvParams& p, cudaStream_t s);
-// A launch that may begin while the previous kernel of the stream is still running (programmatic dependent
-// launch); the kernel must execute griddepcontrol.wait before it touches anything an earlier kernel wrote.
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
-    cudaLaunchConfig_t lc{};
-    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = s;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = at; lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, kern, KArgs(args)...);
-}
 // gemv_umma.cu: single-row tensor-core (tcgen05 block-scaled) kernel; same contract.
 int nvfp4_multi_umma(const GemvParams& p, int M, cudaStream_t s);
 size_t umma_presplit_bytes(int M, int K);
@@ -76,12 +64,8 @@ int nvfp4_multi_umma_ws(const GemvParams& p, int M, void* ws, cudaStream_t s);
 // of scales in GLOBAL memory (job-table launches); nullptr = the maps passed as kernel parameters.
 // bimg != nullptr: the activation rows were already split into their B image (K/256 x 8 KB, rows at a
 // stride of 8) and digit weights gam[M*8] by k_split_rows; x and x2 are then not read.
-// pfw, pfs != nullptr (job-table launches with prefetch sizes): weights and scales of a LATER launch that the
-// CTAs of this job ask the L2 for once their own loads are all requested (an even/odd pair of jobs shares one
-// matrix: the MoE gate and up jobs of a pair prefetch the pair's down matrix).
 struct UmJob { float* y; const float* x; const float* x2; const float* gs; const void* mw; const void* ms;
-               const unsigned char* bimg; const float* gam; int N; int M; int task0; int pad;
-               const unsigned char* pfw; const unsigned char* pfs; };
+               const unsigned char* bimg; const float* gam; int N; int M; int task0; int pad; };
 // One unit of k_split_rows: M rows of x (SwiGLU with x2 when x2 != nullptr) -> bimg, gam.  M = 0: nothing.
 struct SplitJob { const float* x; const float* x2; unsigned char* bimg; float* gam; int M; int pad; };
 int umma_split_launch(const SplitJob* jobs, int n_jobs, int K, float limit, cudaStream_t s);
@@ -97,16 +81,7 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
 int moe_experts_mode(const float* x, const b200_moe_layer* L, float* y, const int32_t* sel, const float* wts,
                      void* ws, int M, cudaStream_t s, int wide);
 int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int N, int K, int R);    // two 128-byte maps, host memory
-// table_early: the table was complete before the PREVIOUS launch of the stream started its dependents (it was
-// written two or more launches upstream and the previous launch waited for that), so the CTAs may read it, and
-// request weights, before their own dependency wait.  pf_w_bytes / pf_s_bytes: sizes of the matrices behind the
-// jobs' pfw / pfs (0: no prefetch).
-// comb: the launch is the MoE down products of single-row (token, slot) jobs, ns consecutive jobs per token, and
-// also takes the gate-weighted sum: y[tok, :] = sum_k wts[tok, k] * product(tok, k) (+ the shared expert's, slot
-// topk).  cnt: stride counters per token, zero before the launch and zero again after it.
-struct UmCombine { float* y; const float* wts; unsigned int* cnt; int topk, ns, stride; };
-int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s,
-                      bool table_early = false, size_t pf_w_bytes = 0, size_t pf_s_bytes = 0, const UmCombine* comb = nullptr);
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s);
 
 // gemm_mxf4.cu: the wide GEMM with both operands in NVFP4 (activations quantised per token first).
 // One job: `rows` activation rows, starting at row `row0` of the quantised activation buffer, against one

@@ -16,7 +16,6 @@
 // row's accumulation order is fixed by (K, lane), nothing else.
 #include "b200_internal.h"
 #include "gemv_core.cuh"
-#include "tma_pipe.cuh"
 #include <cstdio>
 #include <cstdlib>
 
@@ -178,24 +177,15 @@ k_gemm_dense(float* __restrict__ y, const void* __restrict__ W, const float* __r
 // aligned rows.
 template <int M>
 __global__ void __launch_bounds__(GEMV_THREADS)
-k_gemm_dense_row(float* __restrict__ y, const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, int N, int K, int early) {
+k_gemm_dense_row(float* __restrict__ y, const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, int N, int K) {
     __shared__ float part[GEMV_WARPS][M];
     const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4* Wr = reinterpret_cast<const uint4*>(W + (size_t)n * K);
     float acc[M];
     #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
-    // Launched while the previous kernel of the stream may still be running.  With weights declared stable this
-    // thread's first two weight vectors (all of them for K <= 4096) are requested before the dependency wait.
-    pdl_launch_dependents();
-    uint4 pre[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-    if (early) {
-        #pragma unroll
-        for (int q = 0; q < 2; ++q) if ((int)threadIdx.x + q * GEMV_THREADS < (K >> 3)) pre[q] = Wr[threadIdx.x + q * GEMV_THREADS];
-    }
-    pdl_wait_cta();
-    for (int i = threadIdx.x, it = 0; i < (K >> 3); i += GEMV_THREADS, ++it) {
-        const uint4 raw = (early && it < 2) ? pre[it & 1] : Wr[i];
+    for (int i = threadIdx.x; i < (K >> 3); i += GEMV_THREADS) {
+        const uint4 raw = Wr[i];
         const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
         float wf[8];
         #pragma unroll
@@ -425,8 +415,7 @@ static int launch_dense(float* y, const void* W, const float* x, int N, int K, i
     const int eb = dtype == B200_F32 ? 4 : 2;
     const bool vec = (((uintptr_t)W & 15) == 0) && ((((size_t)K * eb) & 15) == 0);
     if (dtype == B200_BF16 && vec && N <= 2048 && K >= 2048) {       // few rows: latency-bound, one CTA per row
-        if (launch_pdl(k_gemm_dense_row<M>, dim3(N), dim3(GEMV_THREADS), 0, s, y, static_cast<const __nv_bfloat16*>(W), x, N, K,
-                       stable_weights_option()) != cudaSuccess) return launch_failed("k_gemm_dense_row");
+        k_gemm_dense_row<M><<<N, GEMV_THREADS, 0, s>>>(y, static_cast<const __nv_bfloat16*>(W), x, N, K);
         return check_launch("k_gemm_dense_row");
     }
     if (dtype == B200_F32) {

@@ -87,10 +87,6 @@ struct UmParams {
     uint32_t bimg_off, scl_off, tsc_off;           // shared-memory offsets of the B image, of the scale slabs and (resident scales) of their transposed copy from the (1 KB aligned) ring
     int ov_first;                                  // resident scales: stages from this one on share their bytes with the scale slabs or the transposed copy
     int early;                                     // stages requested by the producer before it waits for the other barriers (-1: not even the slabs)
-    int table_early;                               // job-table launches: the table may be read before the dependency wait
-    int xgate;                                     // the producer requests only `early` stages until the workers' activation loads have landed
-    uint32_t pf_w_bytes, pf_s_bytes;               // sizes of the matrices behind the jobs' pfw / pfs (0: no prefetch)
-    UmCombine comb;                                // comb.y != nullptr: the MoE gate-weighted sum is taken inside this launch
 };
 
 
@@ -117,7 +113,7 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 // scratch [UM_MAX_M][8]; named barrier 1 is used among the 256.
 template <bool SINGLE>
 __device__ __forceinline__ void split_rows(const float* x, const float* x2, float lim, int M, int K, int stride_m,
-                                           unsigned char* bimg, float* gam, float (*red)[8], int t4, int xbar = 0) {
+                                           unsigned char* bimg, float* gam, float (*red)[8], int t4) {
     const int lane = t4 & 31;
     auto ldx = [&](const float4* row, const float4* row2, int i) -> float4 {
         float4 v = row[i];
@@ -130,8 +126,8 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
         }
         return v;
     };
-    // Pass A: amax of every activation row.  With one row this thread's first 16-group (after the SwiGLU, if
-    // any) stays in registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
+    // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
+    // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
     float4 xv[4];
     for (int m = 0; m < M; ++m) {
         const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
@@ -144,7 +140,7 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 v = ldx(xr, xr2, i + q);
-                if ((SINGLE || M == 1) && i == t4 * 4) xv[q] = v;
+                if (SINGLE && i == t4 * 4) xv[q] = v;
                 a = max(a, max(max(ab(v.x), ab(v.y)), max(ab(v.z), ab(v.w))));
             }
         }
@@ -152,8 +148,6 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
         for (int o = 16; o; o >>= 1) a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
         if (lane == 0) red[m][t4 >> 5] = __uint_as_float(a);
     }
-    // this warp's activation loads have landed: tell the producer warp, which may be waiting for that at named barrier `xbar`
-    if (xbar) asm volatile("bar.arrive %0, %1;" :: "r"(xbar), "r"(UM_WORKERS + 32) : "memory");
     named_sync(1, UM_WORKERS);
     // Pass B: x = gamma * v with |v| < 4; v is kept to 14 fractional bits
     auto row_inv = [&](int m) -> float {
@@ -210,7 +204,7 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
     };
     if (SINGLE || M == 1) {
         const float inv = row_inv(0);
-        for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, g == t4);
+        for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, SINGLE && g == t4);
     } else {
         // two rows per trip: two independent dependency chains for the scheduler to interleave
         for (int m = 0; m < M; m += 2) {
@@ -234,7 +228,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar, bi_bar, scd_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int comb_last_s;
     __shared__ float gam[UM_MAX_M][UM_NB], red[UM_MAX_M][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, nst = K >> 8;               // 256-k steps along K
@@ -242,12 +235,10 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     int ji = 0;
     UmJob J;
     const int T = GEN ? p.T : 1;
-    int pf_piece = 0, pf_pieces = 0;                 // this CTA's share of the matrix its job pair prefetches
     if (GEN && p.table) {
-        if (!p.table_early) pdl_wait_cta();          // the table is written by an earlier kernel of the stream
+        pdl_wait();                                  // the table is written by an earlier kernel of the stream
         const int per_job = p.tiles_per_job / T;     // CTAs per job (the host makes T divide tiles_per_job)
         ji = (int)blockIdx.x / per_job;
-        pf_pieces = 2 * per_job; pf_piece = (ji & 1) * per_job + ((int)blockIdx.x - ji * per_job);
         J = p.table[ji];
         if (J.N <= 0) return;                        // an unused slot of the table: the whole CTA leaves
         J.task0 = ji * per_job;
@@ -361,61 +352,22 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             if (!early_scales) {
                 if (lane == 0) { asm volatile("prefetch.tensormap [%0];" :: "l"(J.mw) : "memory");
                                  asm volatile("prefetch.tensormap [%0];" :: "l"(J.ms) : "memory"); }
-                if (!p.prefetch_before_wait) pdl_wait_warp();
+                if (!p.prefetch_before_wait) pdl_wait();
                 issue_scales();
             }
-            const bool xg = GEN && p.xgate && !J.bimg;
-            if (xg) {
-                // Job-table launches learn their weights and their activations at the same moment.  The activation
-                // row is tiny and everything waits for it: request a few stages, let it through, then the rest.
-                for (int g = lane; g < min(nsteps, min(p.stages, p.early)); g += 32) if (g >= n_early) issue_stage(g);
-                named_sync(6, UM_WORKERS + 32);      // the workers arrive there (split_rows); a hardware barrier needs no initialisation
-            }
             for (int g = lane; g < nsteps; g += 32) {
-                if (g < n_early || (xg && g < min(p.stages, p.early))) continue;
-                // (a suspending wait: up to 20 lanes wait here for different stages, and as a polling loop they
-                // would take the issue slots of the two worker warps that share this warp's scheduler)
-                if (g >= p.stages) mbar_wait(empty0 + (g - p.stages) * 8, 0, p.status, 1);    // the step that had this stage is done
+                if (g < n_early) continue;
+                if (g >= p.stages) UM_WAIT(empty0 + (g - p.stages) * 8, 0, p.status, 1);      // the step that had this stage is done
                 else if (RES && g % p.stages >= p.ov_first) UM_WAIT(smem_u32(&scd_bar), 0, p.status, 8);   // the slabs under this stage are in TMEM
                 issue_stage(g);
             }
             __syncwarp();
-            if (GEN && p.pf_w_bytes && J.pfw) {
-                // All of this CTA's loads are requested: from here on it only drains its ring.  Ask the L2 for
-                // this CTA's share of a later launch's matrix, 16 KB per instruction, the lanes taking turns.
-                auto prefetch = [&](const unsigned char* base, uint32_t total) {
-                    const uint32_t per = ((total + (uint32_t)pf_pieces - 1) / (uint32_t)pf_pieces + 15u) & ~15u;
-                    const uint32_t lo = min(per * (uint32_t)pf_piece, total), hi = min(lo + per, total);
-                    for (uint32_t o = lo + (uint32_t)lane * 16384u; o < hi; o += 32u * 16384u) {
-                        const uint32_t n = min(16384u, hi - o) & ~15u;
-                        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + o), "r"(n) : "memory");
-                    }
-                };
-                prefetch(J.pfw, p.pf_w_bytes);
-                prefetch(J.pfs, p.pf_s_bytes);
-            }
             // Tail: the tcgen05.commit arrivals on empty_bar are asynchronous.  Wait for the last one
             // of every stage, or the CTA could exit with an arrival still in flight and it would
             // land on whatever the next CTA keeps at that shared-memory address.
             for (int g = max(0, nsteps - p.stages) + lane; g < nsteps; g += 32)
-                mbar_wait(empty0 + g * 8, 0, p.status, 5);
+                UM_WAIT(empty0 + g * 8, 0, p.status, 5);
             __syncwarp();
-        }
-        else if (warp == 1 && !p.prefetch_before_wait && !(GEN && p.table) && J.pfw) {
-            // Weights not declared stable: nothing of them may be copied into shared memory before the dependency
-            // wait, but the L2 is the point of coherence, so the CTA's rows (contiguous in memory) can be asked into
-            // the L2 right away, 16 KB per instruction, and the loads after the wait find them there.
-            const int rows = min(p.R * T, J.N - row0);
-            auto prefetch = [&](const unsigned char* base, uint32_t bytes) {
-                for (uint32_t o = (uint32_t)lane * 16384u; o < bytes; o += 32u * 16384u) {
-                    const uint32_t n = min(16384u, bytes - o) & ~15u;
-                    if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + o), "r"(n) : "memory");
-                }
-            };
-            if (rows > 0) {
-                prefetch(J.pfw + (size_t)row0 * (K >> 1), (uint32_t)rows * (uint32_t)(K >> 1));
-                prefetch(J.pfs + (size_t)row0 * (K >> 4), (uint32_t)rows * (uint32_t)(K >> 4));
-            }
         }
         else if (warp == 1 && !GEN) {
             // L2 prefetch of the steps the ring cannot take at once (legal before the upstream kernel
@@ -476,22 +428,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             }
             __syncwarp();
         }
-        // General kernel: these warps are idle while the workers split the activations, so they move the scales of
-        // the steps of the ring's first round (a slot each, free at this point); the workers take over from there.
-        const int npre = RES ? 0 : (min(nsteps, p.stages) & ~1);       // even: the two worker groups keep their parity
-        if (!RES && npre > 0) {
-            UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
-            int t = 0, it = 0;
-            for (int g = 0; g < npre; ++g) {
-                uint4 v[4];
-                load_scales(t, it, v);
-                store_scales((uint32_t)g, v);
-                if (++it == nst) { it = 0; ++t; }
-            }
-        }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
-        for (int g = 0; g < npre; ++g) mbar_arrive(smem_u32(&sf_bar[g]));
         if (RES && warp - UM_LOAD_WARPS < nsteps)        // this warp's first step: its weights are awaited now rather than after the barrier
             UM_WAIT(full0 + (warp - UM_LOAD_WARPS) * 8, 0, p.status, 3);
         const int me = warp - UM_LOAD_WARPS;
@@ -512,7 +450,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 const uint64_t dA = dA0 + (((uint32_t)s * p.stage_bytes) >> 4), dB = dB0 + (uint32_t)(it * p.max_m) * 64u;
                 const uint32_t acc0 = it >= 4;                          // the first k-block of an accumulator starts it
                 UM_WAIT((RES ? full0 : sf0) + g * 8, 0, p.status, 3);      // resident scales: only the step's weights are awaited
-                if (!RES && g < npre) UM_WAIT(full0 + g * 8, 0, p.status, 2);   // scales moved ahead of the weights: wait for those too
                 tc_fence_after();
                 if (lane == 0) {
                     #pragma unroll
@@ -535,7 +472,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
         // ---- workers: activation split, then per-step scale copies; the first four warps also the epilogue ----
         const int t4 = tid - UM_LOADERS - 32 * UM_MMA_WARPS;      // 0..255
         const int q4 = warp & 3;
-        pdl_wait_group(1, UM_WORKERS, t4 == 0);
+        pdl_wait();
         const float gsv = J.gs[0];
         if (GEN && J.bimg) {
             // The B image was split once for all CTAs of the job by k_split_rows: copy it in.
@@ -547,7 +484,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             if (t4 < M * UM_NB) (&gam[0][0])[t4] = J.gam[t4];
             UM_WAIT(smem_u32(&bi_bar), 0, p.status, 7);
         } else {
-            split_rows<!GEN>(J.x, GEN ? J.x2 : nullptr, p.limit, M, K, p.max_m, bimg, &gam[0][0], red, t4, (GEN && p.xgate) ? 6 : 0);
+            split_rows<!GEN>(J.x, GEN ? J.x2 : nullptr, p.limit, M, K, p.max_m, bimg, &gam[0][0], red, t4);
         }
         fence_async_smem();
         tc_fence_before();
@@ -560,12 +497,11 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // go to the TMEM slot of its stage.
             const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
             const int grp = t4 >> 7;
-            const int g0 = (min(nsteps, p.stages) & ~1) + grp;        // the MMA warps moved the steps before that
-            int s = g0 % p.stages;
+            int s = grp % p.stages;
             UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
             // Software-pipelined: the next step's scale bytes are read from shared memory while this
             // step's tcgen05.st is in flight.
-            int rt = g0 / nst, rit = g0 - rt * nst;                    // tile and k-block of the next step to read
+            int rt = grp / nst, rit = grp - rt * nst;                  // tile and k-block of the next step to read
             auto read_scales = [&](int g, uint4 (&v)[4]) {
                 // full[g] also says that the MMAs that last read this stage's scale slot are done
                 UM_WAIT(full0 + g * 8, 0, p.status, 2);
@@ -574,8 +510,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 load_scales(t, it, v);
             };
             uint4 v[4], vn[4];
-            if (g0 < nsteps) read_scales(g0, v);
-            for (int g = g0; g < nsteps; g += 2) {
+            if (grp < nsteps) read_scales(grp, v);
+            for (int g = grp; g < nsteps; g += 2) {
                 store_scales((uint32_t)s, v);
                 if (g + 2 < nsteps) read_scales(g + 2, vn);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -612,35 +548,6 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                             acc = fmaf(dsum, gam[m][dg], acc);
                         }
                         J.y[(size_t)m * J.N + row] = acc / gsv;
-                    }
-                }
-            }
-            if (GEN && p.comb.y) {
-                // MoE down products, one single-row job per (token, slot) pair: the CTA that finishes LAST among
-                // the pairs of a token for this range of rows takes the gate-weighted sum over the slots, in slot
-                // order and with the arithmetic of k_moe_combine, so the result does not depend on which CTA that was.
-                const int per_job = p.tiles_per_job / T, tok = ji / p.comb.ns;
-                unsigned int* cnt = p.comb.cnt + (size_t)tok * p.comb.stride + ((int)blockIdx.x - ji * per_job);
-                __threadfence();
-                named_sync(5, 128);
-                if (t4 == 0) {
-                    const unsigned int old = atomicAdd(cnt, 1u);
-                    comb_last_s = old == (unsigned int)p.comb.ns - 1u;
-                    if (comb_last_s) *cnt = 0u;          // ready for the next call
-                    __threadfence();
-                }
-                named_sync(5, 128);
-                if (comb_last_s) {
-                    const float* part0 = J.y - (size_t)ji * J.N + (size_t)tok * p.comb.ns * J.N;      // the token's first pair
-                    const float* w = p.comb.wts + (size_t)tok * p.comb.topk;
-                    for (int t = 0; t < T; ++t) {
-                        const int row = row0 + t * p.R + r;
-                        if (r < p.R && row < J.N) {
-                            float acc = 0.f;
-                            for (int k = 0; k < p.comb.topk; ++k) acc = fmaf(__ldcg(w + k), __ldcg(part0 + (size_t)k * J.N + row), acc);
-                            if (p.comb.ns > p.comb.topk) acc += __ldcg(part0 + (size_t)p.comb.topk * J.N + row);
-                            p.comb.y[(size_t)tok * J.N + row] = acc;
-                        }
                     }
                 }
             }
@@ -762,8 +669,7 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
     for (int i = 0; i < g.n_jobs; ++i) {
         p.j[i] = UmJob{g.j[i].y + (size_t)m0 * g.j[i].N, g.j[i].x + (size_t)m0 * K, nullptr, g.j[i].gs, nullptr, nullptr,
                        pre ? pre->img + (size_t)pre->chunk * pre->chunk_bytes : nullptr,
-                       pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0,
-                       static_cast<const unsigned char*>(g.j[i].P), static_cast<const unsigned char*>(g.j[i].S)};
+                       pre ? pre->gam + (size_t)pre->chunk * UM_MAX_M * UM_NB : nullptr, g.j[i].N, M, tasks, 0};
         tasks += ((g.j[i].N + R - 1) / R + p.T - 1) / p.T;
         if (!make_map(&maps.w[i], g.j[i].P, g.j[i].N, (size_t)K / 2, 128, R, true) ||
             !make_map(&maps.s[i], g.j[i].S, g.j[i].N, (size_t)K / 16, p.sc_box, R, p.sc_swz != 0)) return B200_ENOTIMPL;
@@ -887,17 +793,10 @@ int umma_encode_maps(void* out_w, void* out_s, const void* P, const void* S, int
 
 // n_jobs jobs of N weight rows and up to max_m activation rows each, described by `table` (device memory, filled by an earlier
 // kernel of the stream); every job's tensor maps were encoded with box height R.
-int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s,
-                      bool table_early, size_t pf_w_bytes, size_t pf_s_bytes, const UmCombine* comb) {
+int umma_table_launch(const UmJob* table, int n_jobs, int N, int K, int R, float limit, int max_m, cudaStream_t s) {
     static UmMaps none{};                            // unused in table mode, still a kernel parameter
     UmParams p{};
     p.table = table; p.limit = limit; p.n_jobs = n_jobs; p.K = K; p.R = R; p.max_m = max_m;
-    p.table_early = table_early ? 1 : 0; p.pf_w_bytes = (uint32_t)pf_w_bytes; p.pf_s_bytes = (uint32_t)pf_s_bytes;
-    { static const int xg = [] { const char* e = getenv("B200_GEMV_XGATE"); return e ? atoi(e) : 1; }(); p.xgate = (xg && max_m == 1) ? 1 : 0; }
-    if (comb) {
-        if (max_m != 1 || (N + R - 1) / R > comb->stride) return B200_ENOTIMPL;
-        p.comb = *comb;
-    }
     p.tiles_per_job = (N + R - 1) / R;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     // Tiles per CTA: as many as still leave every SM a CTA.  A CTA splits its activation row and

@@ -16,7 +16,6 @@
 #include "b200_internal.h"
 #include "gemv_core.cuh"
 #include "moe_plan.cuh"
-#include "tma_pipe.cuh"
 #include <cstdio>
 
 namespace b200 {
@@ -35,47 +34,37 @@ struct MoeArgs {
 // among equal ranking values the lowest expert index wins, as in the reference's serial scan
 // with a strict '>' (kernels/moe.cu:146-152).
 template <int C>                                   // candidates per lane: n_expert <= 32 * C
-__device__ __forceinline__ void route_token(int tok, int lane, int32_t* __restrict__ sel, float* __restrict__ wts,
-                                            const float* __restrict__ logits, const float* __restrict__ bias, int E, int K,
-                                            float scaling, int norm_prob, const MoePlan& plan) {
+__global__ void __launch_bounds__(32)
+k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restrict__ logits,
+        const float* __restrict__ bias, int E, int K, float scaling, int norm_prob, const __grid_constant__ MoePlan plan) {
+    const int tok = blockIdx.x, lane = threadIdx.x;
     logits += (size_t)tok * E; sel += (size_t)tok * K; wts += (size_t)tok * K;
-    // Ranking values as unsigned keys that order like the floats (0 = not a candidate: padding, a NaN, anything
-    // at or below -1e30, or already taken), so that a round is two warp reductions -- the largest key, then the
-    // lowest expert index among the lanes that hold it -- instead of five rounds of three shuffles.
-    float score[C];
-    uint32_t key[C];
+    float score[C], choice[C];
     #pragma unroll
     for (int j = 0; j < C; ++j) {
         const int i = lane + 32 * j;
-        score[j] = 0.f; key[j] = 0u;
         if (i < E) {
-            score[j] = 1.f / (1.f + __expf(-__ldcg(logits + i)));       // from L2: other CTAs of the launch may have written them
-            const float c = score[j] + bias[i];
-            const uint32_t u = __float_as_uint(c);
-            if (c > -1e30f) key[j] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-        }
+            score[j] = 1.f / (1.f + __expf(-logits[i]));
+            choice[j] = score[j] + bias[i];
+        } else { score[j] = 0.f; choice[j] = -3.0e38f; }
     }
-    uint32_t lk = 0u; int lj = 0; float ls = 0.f;   // this lane's best candidate: key, slot, gate value (lowest slot among equals)
-    auto local_best = [&]() {
-        lk = 0u; lj = 0; ls = 0.f;
-        #pragma unroll
-        for (int j = 0; j < C; ++j) if (key[j] > lk) { lk = key[j]; lj = j; ls = score[j]; }
-    };
-    local_best();
     float my_w = 0.f;                              // lane k keeps the k-th gate
     int my_e = 0;                                  // ... and the k-th expert
     for (int k = 0; k < K; ++k) {
-        const uint32_t gmax = __reduce_max_sync(0xffffffffu, lk);
-        int bi = 0; float bs = 0.f;                // fewer than K candidates: expert 0 with gate 0, as the serial scan would leave it
-        if (gmax) {
-            bi = (int)__reduce_min_sync(0xffffffffu, lk == gmax ? (uint32_t)(lane + 32 * lj) : 0x7fffffffu);
-            bs = __shfl_sync(0xffffffffu, ls, bi & 31);
+        float bv = -1e30f, bs = 0.f; int bi = 0x7fffffff;
+        #pragma unroll
+        for (int j = 0; j < C; ++j)
+            if (choice[j] > bv) { bv = choice[j]; bs = score[j]; bi = lane + 32 * j; }
+        #pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bs = os; bi = oi; }
         }
-        if (lane == (bi & 31)) {
-            #pragma unroll
-            for (int j = 0; j < C; ++j) if (j == (bi >> 5)) key[j] = 0u;
-            local_best();
-        }
+        if (bi >= E) bi = 0;                       // only if fewer than K finite candidates
+        #pragma unroll
+        for (int j = 0; j < C; ++j) if (lane + 32 * j == bi) choice[j] = -1e30f;
         if (lane == k) { my_w = bs; my_e = bi; }
         if (lane == 0) sel[k] = bi;
     }
@@ -87,96 +76,6 @@ __device__ __forceinline__ void route_token(int tok, int lane, int32_t* __restri
     if (lane < K) wts[lane] = my_w / d * scaling;
     // job records of the tensor-core experts for this token's pairs (prepared layers only)
     if (plan.j1 && lane < plan.ns) moe_plan_pair(plan, tok, lane, my_e);
-    if (plan.j1 && plan.comb_cnt)
-        for (int i = lane; i < plan.comb_stride; i += 32) plan.comb_cnt[(size_t)tok * plan.comb_stride + i] = 0u;
-}
-
-template <int C>
-__global__ void __launch_bounds__(32)
-k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restrict__ logits,
-        const float* __restrict__ bias, int E, int K, float scaling, int norm_prob, const __grid_constant__ MoePlan plan) {
-    pdl_launch_dependents();
-    pdl_wait_warp();                               // launched while the logits may still be running
-    route_token<C>((int)blockIdx.x, (int)threadIdx.x, sel, wts, logits, bias, E, K, scaling, norm_prob, plan);
-}
-
-// Router logits and routing in ONE launch for up to 8 tokens: CTA n computes the logits of expert n for every
-// token -- the arithmetic of k_gemm_dense_row (gemv.cu), bit for bit -- and the CTA that finishes last routes
-// the tokens, one warp each (what k_route does).  `done` counts finished CTAs; the last one sets it back to 0.
-__device__ unsigned int g_router_done[64];
-template <int C>
-__global__ void __launch_bounds__(GEMV_THREADS)
-k_router_fused(float* __restrict__ logits, const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, int M, int Kh, int early,
-               unsigned int* __restrict__ done, int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restrict__ bias,
-               int topk, float scaling, int norm_prob, const __grid_constant__ MoePlan plan) {
-    __shared__ float part[GEMV_WARPS][8];
-    __shared__ int last_s;
-    const int n = blockIdx.x, E = gridDim.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint4* Wr = reinterpret_cast<const uint4*>(W + (size_t)n * Kh);
-    float acc[8];
-    #pragma unroll
-    for (int m = 0; m < 8; ++m) acc[m] = 0.f;
-    pdl_launch_dependents();
-    if (plan.j1 && plan.shared && threadIdx.x < 6) {
-        // The shared expert runs for every token: its three matrices are asked into the L2 now, a slice per CTA,
-        // while memory is otherwise idle (the L2 is the point of coherence: legal before the dependency wait).
-        const b200_nvfp4_mat mt = plan.shared[threadIdx.x >> 1];
-        const bool sc = threadIdx.x & 1;
-        const size_t total = (size_t)plan.H * plan.I / (sc ? 16 : 2);
-        const size_t per = ((total + E - 1) / E + 15) & ~(size_t)15, lo = min(per * n, total), hi = min(lo + per, total);
-        const unsigned char* base = static_cast<const unsigned char*>(sc ? (const void*)mt.scale : (const void*)mt.packed);
-        for (size_t o = lo; o < hi; o += 16384) {
-            const uint32_t nb = (uint32_t)min((size_t)16384, hi - o) & ~15u;
-            if (nb) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + o), "r"(nb) : "memory");
-        }
-    }
-    uint4 pre[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-    if (early) {                                   // router weights declared stable: requested before the dependency wait
-        #pragma unroll
-        for (int q = 0; q < 2; ++q) if ((int)threadIdx.x + q * GEMV_THREADS < (Kh >> 3)) pre[q] = Wr[threadIdx.x + q * GEMV_THREADS];
-    }
-    pdl_wait_cta();
-    for (int i = threadIdx.x, it = 0; i < (Kh >> 3); i += GEMV_THREADS, ++it) {
-        const uint4 raw = (early && it < 2) ? pre[it & 1] : Wr[i];
-        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        float wf[8];
-        #pragma unroll
-        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
-        #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            if (m < M) {
-                const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * Kh + (size_t)i * 8);
-                const float4 a = xr[0], b = xr[1];
-                const float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-                #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[m] = fmaf(wf[j], xv[j], acc[m]);
-            }
-        }
-    }
-    #pragma unroll
-    for (int m = 0; m < 8; ++m) {
-        if (m < M) {
-            const float v = warp_sum(acc[m]);
-            if (lane == 0) part[warp][m] = v;
-        }
-    }
-    __syncthreads();
-    if ((int)threadIdx.x < M) {
-        float v = 0.f;
-        #pragma unroll
-        for (int w = 0; w < GEMV_WARPS; ++w) v += part[w][threadIdx.x];
-        logits[(size_t)threadIdx.x * E + n] = v;
-        __threadfence();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int old = atomicAdd(done, 1u);
-        last_s = old == (unsigned int)E - 1u;
-        if (last_s) *done = 0u;
-        __threadfence();
-    }
-    __syncthreads();
-    if (last_s && warp < M) route_token<C>(warp, lane, sel, wts, logits, bias, E, topk, scaling, norm_prob, plan);
 }
 
 template <int MATH>
@@ -361,32 +260,13 @@ static int route_launch(const float* x, const b200_moe_layer* L, int32_t* sel, f
                         cudaStream_t stream, const MoePlan& plan) {
     if (int rc = check_layer(L, M)) return rc;
     if (!x || !sel || !wts || !logits || !L->router_bias) return B200_EINVAL;
-    const b200_wref& rw = L->router_w;
-    if (M <= 8 && M <= GEMV_WARPS && L->n_expert <= 32 * ROUTE_MAXC && !rw.packed && rw.p && !((uintptr_t)rw.p & 15) && !((uintptr_t)x & 15) && !(L->hidden & 7) &&
-        L->hidden >= 2048) {
-        // one launch; the shapes are those for which the separate logits launch would run k_gemm_dense_row
-        static unsigned int* done_base[64] = {nullptr};
-        static unsigned int next_slot = 0;
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return launch_failed("moe_route: cudaGetDevice");
-        if (!done_base[dev]) {
-            void* ptr = nullptr;
-            if (cudaGetSymbolAddress(&ptr, g_router_done) != cudaSuccess) return launch_failed("moe_route: cudaGetSymbolAddress");
-            done_base[dev] = static_cast<unsigned int*>(ptr);
-        }
-        // calls in flight at the same time (different streams) must not share a counter: 64 of them in rotation
-        unsigned int* done = done_base[dev] + (__atomic_fetch_add(&next_slot, 1u, __ATOMIC_RELAXED) & 63u);
-        auto fk = L->n_expert <= 128 ? k_router_fused<4> : L->n_expert <= 256 ? k_router_fused<8> : k_router_fused<ROUTE_MAXC>;
-        credit(B200_CREDIT_GEMM, (double)L->n_expert * L->hidden * 2.0);
-        if (launch_pdl(fk, dim3(L->n_expert), dim3(GEMV_THREADS), 0, stream, logits, static_cast<const __nv_bfloat16*>(rw.p), x, M, L->hidden,
-                       stable_weights_option(), done, sel, wts, L->router_bias, L->topk, L->routed_scale, L->norm_topk, plan) != cudaSuccess)
-            return launch_failed("k_router_fused");
-        return check_launch("k_router_fused");
-    }
     if (int rc = b200_nvfp4_gemm(logits, &L->router_w, x, M, L->n_expert, L->hidden, B200_BF16, stream)) return rc;
-    auto kern = L->n_expert <= 128 ? k_route<4> : L->n_expert <= 256 ? k_route<8> : k_route<ROUTE_MAXC>;
-    if (launch_pdl(kern, dim3(M), dim3(32), 0, stream, sel, wts, (const float*)logits, L->router_bias, L->n_expert, L->topk,
-                   L->routed_scale, L->norm_topk, plan) != cudaSuccess) return launch_failed("k_route");
+    if (L->n_expert <= 128)
+        k_route<4><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
+    else if (L->n_expert <= 256)
+        k_route<8><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
+    else
+        k_route<ROUTE_MAXC><<<M, 32, 0, stream>>>(sel, wts, logits, L->router_bias, L->n_expert, L->topk, L->routed_scale, L->norm_topk, plan);
     return check_launch("k_route");
 }
 

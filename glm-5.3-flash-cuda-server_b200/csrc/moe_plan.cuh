@@ -12,7 +12,6 @@ struct MoePlan {
     const unsigned char* maps;                     // [(E + 1) experts][gate w,s | up w,s | down w,s] x 128 bytes
     const float* x; float* gbuf; float* ubuf; float* part;
     int topk, ns, E, H, I;
-    unsigned int* comb_cnt; int comb_stride;       // counters of the combine inside the down launch: [tokens][comb_stride], zeroed with the plan
 };
 
 // Pair (token m, slot): slot < topk is routed expert e, slot == topk the shared expert.
@@ -25,12 +24,9 @@ __device__ __forceinline__ void moe_plan_pair(const MoePlan& q, int m, int slot,
     const float* xm = q.x + (size_t)m * q.H;
     float* g = q.gbuf + (size_t)pair * q.I;
     float* u = q.ubuf + (size_t)pair * q.I;
-    // the gate and up jobs of the pair ask the L2 for the pair's down matrix (see UmJob)
-    const unsigned char* dw = static_cast<const unsigned char*>(mats[2].packed);
-    const unsigned char* ds = static_cast<const unsigned char*>(mats[2].scale);
-    q.j1[2 * pair] = UmJob{g, xm, nullptr, mats[0].gscale, mp, mp + 128, nullptr, nullptr, q.I, 1, 0, 0, dw, ds};
-    q.j1[2 * pair + 1] = UmJob{u, xm, nullptr, mats[1].gscale, mp + 256, mp + 384, nullptr, nullptr, q.I, 1, 0, 0, dw, ds};
-    q.j2[pair] = UmJob{q.part + (size_t)pair * q.H, g, u, mats[2].gscale, mp + 512, mp + 640, nullptr, nullptr, q.H, 1, 0, 0, nullptr, nullptr};
+    q.j1[2 * pair] = UmJob{g, xm, nullptr, mats[0].gscale, mp, mp + 128, nullptr, nullptr, q.I, 1, 0, 0};
+    q.j1[2 * pair + 1] = UmJob{u, xm, nullptr, mats[1].gscale, mp + 256, mp + 384, nullptr, nullptr, q.I, 1, 0, 0};
+    q.j2[pair] = UmJob{q.part + (size_t)pair * q.H, g, u, mats[2].gscale, mp + 512, mp + 640, nullptr, nullptr, q.H, 1, 0, 0};
 }
 
 }  // namespace b200

@@ -77,7 +77,6 @@ static int pick_rows(int n_jobs, int N) {
 
 __global__ void k_moe_plan(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, int M) {
     const int pair = blockIdx.x * blockDim.x + threadIdx.x;
-    if (q.comb_cnt) for (int i = pair; i < M * q.comb_stride; i += gridDim.x * blockDim.x) q.comb_cnt[i] = 0u;
     if (pair >= M * q.ns) return;
     const int m = pair / q.ns, slot = pair - m * q.ns;
     moe_plan_pair(q, m, slot, slot < q.topk ? sel[(size_t)m * q.topk + slot] : 0);
@@ -89,8 +88,6 @@ __global__ void k_moe_combine(float* __restrict__ y, const float* __restrict__ p
                               const int* __restrict__ posof, int M, int topk, int ns, int H) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;          // float4 index
     const int per = H >> 2;
-    pdl_launch_dependents();
-    pdl_wait_cta();                                   // may be launched while the down products are still running
     if (i >= M * per) return;
     const int m = i / per, h4 = i - m * per;
     const float4* p = reinterpret_cast<const float4*>(part) + h4;
@@ -160,13 +157,13 @@ k_moe_group(const __grid_constant__ MoePlan q, const int32_t* __restrict__ sel, 
             float* ga2 = gam2 + (size_t)idx * 64;
             s1[idx] = SplitJob{xg + pos0 * q.H, nullptr, b1, ga1, rows, 0};
             s2[idx] = SplitJob{g, u, b2, ga2, rows, 0};
-            q.j1[2 * idx] = UmJob{g, nullptr, nullptr, mats[0].gscale, mp, mp + 128, b1, ga1, q.I, rows, 0, 0, nullptr, nullptr};
-            q.j1[2 * idx + 1] = UmJob{u, nullptr, nullptr, mats[1].gscale, mp + 256, mp + 384, b1, ga1, q.I, rows, 0, 0, nullptr, nullptr};
-            q.j2[idx] = UmJob{q.part + pos0 * q.H, nullptr, nullptr, mats[2].gscale, mp + 512, mp + 640, b2, ga2, q.H, rows, 0, 0, nullptr, nullptr};
+            q.j1[2 * idx] = UmJob{g, nullptr, nullptr, mats[0].gscale, mp, mp + 128, b1, ga1, q.I, rows, 0, 0};
+            q.j1[2 * idx + 1] = UmJob{u, nullptr, nullptr, mats[1].gscale, mp + 256, mp + 384, b1, ga1, q.I, rows, 0, 0};
+            q.j2[idx] = UmJob{q.part + pos0 * q.H, nullptr, nullptr, mats[2].gscale, mp + 512, mp + 640, b2, ga2, q.H, rows, 0, 0};
         }
     }
     for (int idx = total_jobs + threadIdx.x; idx < max_jobs; idx += blockDim.x) {
-        const UmJob none{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, nullptr, nullptr};
+        const UmJob none{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
         q.j1[2 * idx] = none; q.j1[2 * idx + 1] = none; q.j2[idx] = none;
         s1[idx] = SplitJob{nullptr, nullptr, nullptr, nullptr, 0, 0}; s2[idx] = s1[idx];
     }
@@ -194,8 +191,7 @@ size_t moe_umma_ws_bytes(const b200_moe_layer* L, int M) {
     const size_t ns = (size_t)L->topk + 1, pairs = (size_t)M * ns;
     size_t small = 0;
     if (M <= MU_MAX_TOKENS)
-        small = std::max(moe_gx_ws_bytes(L, M), up256(pairs * 3 * sizeof(UmJob)) + up256((size_t)M * ((L->hidden + 31) / 32) * 4) +
-                                                2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4));
+        small = std::max(moe_gx_ws_bytes(L, M), up256(pairs * 3 * sizeof(UmJob)) + 2 * up256(pairs * L->inter * 4) + up256(pairs * L->hidden * 4));
     const size_t mj = (size_t)grouped_max_jobs(L, M);
     return std::max(std::max(small, moe_gx_ws_bytes(L, M)), up256(pairs * 4) + up256(mj * 3 * sizeof(UmJob)) + 2 * up256(mj * sizeof(SplitJob)) + 2 * up256(mj * 64 * 4) +
            up256(mj * (L->hidden >> 8) * 8192) + up256(mj * (L->inter >> 8) * 8192) +
@@ -214,8 +210,6 @@ int moe_umma_plan_args(const float* x, const b200_moe_layer* L, void* scratch, i
     q->j1 = reinterpret_cast<UmJob*>(w);
     q->j2 = q->j1 + (size_t)2 * pairs;
     w += up256((size_t)M * (L->topk + 1) * 3 * sizeof(UmJob));
-    q->comb_stride = (H + 31) / 32;
-    q->comb_cnt = reinterpret_cast<unsigned int*>(w); w += up256((size_t)M * q->comb_stride * 4);
     q->gbuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
     q->ubuf = reinterpret_cast<float*>(w); w += up256((size_t)M * (L->topk + 1) * I * 4);
     q->part = reinterpret_cast<float*>(w);
@@ -391,16 +385,11 @@ int moe_umma_experts(const float* x, const b200_moe_layer* L, float* y, const in
         k_moe_plan<<<(pairs + 127) / 128, 128, 0, s>>>(q, sel, M);
         if (int rc = check_launch("k_moe_plan")) return rc;
     }
-    // The gate + up launch asks the L2 for the down matrices once its own loads are out, so that memory keeps
-    // streaming through its tail, the turn-over of the SMs and the next launch's activation split; the down
-    // launch reads its job table (written two launches upstream) and requests weights before its dependency wait.
-    // (only while the down matrices of all pairs are a fraction of the L2: 64 MB)
-    const bool pf = (double)pairs * q.H * q.I * 0.5625 <= 64.0e6;
-    if (int rc = umma_table_launch(q.j1, 2 * pairs, q.I, q.H, R_gu, 0.f, 1, s, false, pf ? (size_t)q.H * q.I / 2 : 0, pf ? (size_t)q.H * q.I / 16 : 0)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
-    // ... and takes the gate-weighted sum itself: the last CTA to finish a token's range of rows adds the slots up.
-    const UmCombine comb{y, wts, q.comb_cnt, q.topk, q.ns, q.comb_stride};
-    const int rc = umma_table_launch(q.j2, pairs, q.H, q.I, R_d, L->swiglu_limit, 1, s, true, 0, 0, &comb);
-    return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_table_launch(q.j1, 2 * pairs, q.I, q.H, R_gu, 0.f, 1, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    if (int rc = umma_table_launch(q.j2, pairs, q.H, q.I, R_d, L->swiglu_limit, 1, s)) return rc == B200_ENOTIMPL ? B200_ELAUNCH : rc;
+    const int n4 = M * (q.H >> 2);
+    k_moe_combine<<<(n4 + 255) / 256, 256, 0, s>>>(y, q.part, wts, nullptr, M, q.topk, q.ns, q.H);
+    return check_launch("k_moe_combine");
 }
 
 }  // namespace b200

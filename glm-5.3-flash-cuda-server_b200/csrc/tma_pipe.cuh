@@ -87,10 +87,5 @@ __device__ __forceinline__ void named_sync(int id, int count) {
 // Programmatic dependent launch: wait for the upstream grid's memory, release the downstream.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-// The wait executed by ONE thread while the rest of the group blocks at a hardware barrier: a CTA that is resident
-// early, beside the kernel it depends on, then costs that kernel no issue slots while it waits.
-__device__ __forceinline__ void pdl_wait_cta() { if (threadIdx.x == 0) pdl_wait(); __syncthreads(); }
-__device__ __forceinline__ void pdl_wait_warp() { if ((threadIdx.x & 31) == 0) pdl_wait(); __syncwarp(); }
-__device__ __forceinline__ void pdl_wait_group(int barrier_id, int count, bool leader) { if (leader) pdl_wait(); named_sync(barrier_id, count); }
 
 }  // namespace b200
