@@ -77,28 +77,31 @@ k_quantize(const __nv_bfloat16* __restrict__ w, size_t n_groups, const float* __
     size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (vec_in) {
         const uint4* wv = reinterpret_cast<const uint4*>(w);
-        for (; g + stride < n_groups; g += 2 * stride) {         // two groups per trip: four loads in flight, two chains
-            const uint4 a0 = wv[2 * g], b0 = wv[2 * g + 1], a1 = wv[2 * (g + stride)], b1 = wv[2 * (g + stride) + 1];
-            float v0[16], v1[16];
-            unpack_bf16x16(a0, b0, v0); unpack_bf16x16(a1, b1, v1);
+        // Two groups per trip: four loads in flight, two chains.  The tensor is walked from its END: the amax pass
+        // that ran just before read it front to back, so its tail is what the L2 still holds.
+        for (; g + stride < n_groups; g += 2 * stride) {
+            const size_t ga = n_groups - 1 - g, gb = n_groups - 1 - (g + stride);
+            const uint4 a0 = wv[2 * ga], b0 = wv[2 * ga + 1], a1 = wv[2 * gb], b1 = wv[2 * gb + 1];
+            const uint32_t u0[8] = {a0.x, a0.y, a0.z, a0.w, b0.x, b0.y, b0.z, b0.w}, u1[8] = {a1.x, a1.y, a1.z, a1.w, b1.x, b1.y, b1.z, b1.w};
             uint32_t lo0, hi0, lo1, hi1; int c0, c1;
-            quantize_group(v0, gs, lo0, hi0, c0);
-            quantize_group(v1, gs, lo1, hi1, c1);
-            store_group(packed, scale, g, lo0, hi0, c0, vec_out);
-            store_group(packed, scale, g + stride, lo1, hi1, c1, vec_out);
+            quantize_group_bf16(u0, gs, lo0, hi0, c0);
+            quantize_group_bf16(u1, gs, lo1, hi1, c1);
+            store_group(packed, scale, ga, lo0, hi0, c0, vec_out);
+            store_group(packed, scale, gb, lo1, hi1, c1, vec_out);
         }
     }
     for (; g < n_groups; g += stride) {
+        const size_t gr = vec_in ? n_groups - 1 - g : g;
         float v[16];
         if (vec_in) {
-            unpack_bf16x16(reinterpret_cast<const uint4*>(w)[2 * g], reinterpret_cast<const uint4*>(w)[2 * g + 1], v);
+            unpack_bf16x16(reinterpret_cast<const uint4*>(w)[2 * gr], reinterpret_cast<const uint4*>(w)[2 * gr + 1], v);
         } else {
             #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(w[16 * g + j]);
+            for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(w[16 * gr + j]);
         }
         uint32_t lo, hi; int code;
         quantize_group(v, gs, lo, hi, code);
-        store_group(packed, scale, g, lo, hi, code, vec_out);
+        store_group(packed, scale, gr, lo, hi, code, vec_out);
     }
 }
 
