@@ -25,19 +25,26 @@ k_amax_bf16(const uint4* __restrict__ w, size_t n_vec, const __nv_bfloat16* __re
     float a = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // packed: |x| as bit patterns, __hmax2 (which, like fmaxf, returns the other operand when one is a NaN)
+    uint32_t mbits = 0u;
     auto fold = [&](const uint4& v) {
         const uint32_t u[4] = {v.x, v.y, v.z, v.w};
         #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            a = fmaxf(a, fabsf(__uint_as_float(u[j] << 16)));
-            a = fmaxf(a, fabsf(__uint_as_float(u[j] & 0xffff0000u)));
+            const uint32_t x = u[j] & 0x7fff7fffu;
+            const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&mbits), *reinterpret_cast<const __nv_bfloat162*>(&x));
+            mbits = *reinterpret_cast<const uint32_t*>(&r);
         }
     };
-    for (; i + 3 * stride < n_vec; i += 4 * stride) {           // four loads in flight per thread
-        const uint4 v0 = w[i], v1 = w[i + stride], v2 = w[i + 2 * stride], v3 = w[i + 3 * stride];
-        fold(v0); fold(v1); fold(v2); fold(v3);
+    for (; i + 7 * stride < n_vec; i += 8 * stride) {           // eight loads in flight per thread
+        uint4 v[8];
+        #pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = w[i + q * stride];
+        #pragma unroll
+        for (int q = 0; q < 8; ++q) fold(v[q]);
     }
     for (; i < n_vec; i += stride) fold(w[i]);
+    a = fmaxf(fmaxf(0.f, __uint_as_float(mbits << 16)), __uint_as_float(mbits & 0xffff0000u));
     if (blockIdx.x == 0)
         for (size_t i = threadIdx.x; i < n_tail; i += blockDim.x) a = fmaxf(a, fabsf(__bfloat162float(tail[i])));
     a = warp_max(a);

@@ -66,27 +66,22 @@ __device__ __forceinline__ void quantize_group(const float (&v)[16], float gs, u
 // The same group for bf16 inputs, two elements per instruction.  u[j] holds elements 2j (low half) and 2j+1 as
 // they lie in memory.  A bf16 magnitude a exceeds an fp32 threshold t >= 0 exactly when it exceeds t rounded DOWN
 // to bf16 (a is on the bf16 grid: the next grid point above floor(t) is above t), so the seven comparisons run on
-// packed bf16 pairs; each answers 1.0 or 0.0, and their sum on top of 128.0 is the bf16 number 0x4300 + count
-// (a step of 1 at that exponent), so the count is read off the low three bits.  Bit for bit quantize_group.
+// packed bf16 pairs; each answers 1.0 or 0.0.  Summed on top of 128.0, plus 8.0 where the element is negative and
+// its count is not zero, they give the bf16 number 0x4300 + code (a step of 1 at that exponent): the e2m1 code is
+// the low byte.  Comparisons, sums and the sign all run on the half-precision pipe; the integer pipe only takes
+// the magnitudes and gathers the bytes.  Bit for bit quantize_group.
 __device__ __forceinline__ void quantize_group_bf16(const uint32_t (&u)[8], float gs, uint32_t& lo, uint32_t& hi, int& code) {
-    uint32_t a[8];
+    auto bf2 = [](uint32_t v) { return *reinterpret_cast<const __nv_bfloat162*>(&v); };
+    auto bits = [](__nv_bfloat162 v) { return *reinterpret_cast<const uint32_t*>(&v); };
+    __nv_bfloat162 a[8];
     #pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = u[j] & 0x7fff7fffu;
-    // amax: magnitudes order like their bit patterns, per 16-bit half
-    uint32_t m = a[0];
+    for (int j = 0; j < 8; ++j) a[j] = bf2(u[j] & 0x7fff7fffu);
+    // amax: __hmax2 returns the other operand when one is a NaN, as fmaxf does
+    __nv_bfloat162 m = a[0];
     #pragma unroll
-    for (int j = 1; j < 8; ++j) m = __vmaxu2(m, a[j]);
-    const uint32_t mh = max(m & 0xffffu, m >> 16);
-    // a NaN in the group: the float maximum of the reference's code ignores it unless... keep fp32 semantics: fmaxf drops NaNs
-    float amax = 0.f;
-    if (mh <= 0x7f80u) amax = __uint_as_float(mh << 16);
-    else {
-        #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            amax = fmaxf(amax, __uint_as_float(a[j] << 16));
-            amax = fmaxf(amax, __uint_as_float(a[j] & 0xffff0000u));
-        }
-    }
+    for (int j = 1; j < 8; ++j) m = __hmax2(m, a[j]);
+    const uint32_t mb = bits(m);
+    const float amax = fmaxf(fmaxf(0.f, __uint_as_float(mb << 16)), __uint_as_float(mb & 0xffff0000u));
     float s = __fmul_rn(__fdiv_rn(amax, 6.0f), gs);
     s = fminf(fmaxf(s, 0.f), 448.f);
     code = e4m3_floor_code(s);
@@ -96,27 +91,29 @@ __device__ __forceinline__ void quantize_group_bf16(const uint32_t (&u)[8], floa
     }
     const float eff = fmaxf(__fdiv_rn(e4m3_to_f32(code), gs), 1e-30f);
     const double de = (double)eff;
-    auto thr = [&](double mid_plus) -> __nv_bfloat162 {
-        const uint32_t b = __float_as_uint(__double2float_rd(de * mid_plus)) >> 16;      // truncation = rounding down (t >= 0)
-        const uint32_t p = b | (b << 16);
-        return *reinterpret_cast<const __nv_bfloat162*>(&p);
+    auto thr = [&](double mid_plus) {
+        const uint32_t b = __float_as_uint(__double2float_rd(de * mid_plus));      // truncation to bf16 = rounding down (t >= 0)
+        return bf2(__byte_perm(b, b, 0x3232));                                     // the high half in both halves
     };
     const __nv_bfloat162 t0 = thr(0.25 + 0x1p-26), t1 = thr(0.75 + 0x1p-25), t2 = thr(1.25 + 0x1p-24), t3 = thr(1.75 + 0x1p-24),
                          t4 = thr(2.5 + 0x1p-23), t5 = thr(3.5 + 0x1p-23), t6 = thr(5.0 + 0x1p-22);
-    const uint32_t base_bits = 0x43004300u;                                                  // 128.0 | 128.0
-    const __nv_bfloat162 base = *reinterpret_cast<const __nv_bfloat162*>(&base_bits);
-    lo = 0; hi = 0;
+    const __nv_bfloat162 base = bf2(0x43004300u), eight = bf2(0x41004100u), zero = bf2(0u);      // 128.0, 8.0, 0.0
+    uint32_t n[8];
     #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const __nv_bfloat162 av = *reinterpret_cast<const __nv_bfloat162*>(&a[j]);
-        __nv_bfloat162 c = __hadd2(base, __hgt2(av, t0));
-        c = __hadd2(c, __hgt2(av, t1)); c = __hadd2(c, __hgt2(av, t2)); c = __hadd2(c, __hgt2(av, t3));
-        c = __hadd2(c, __hgt2(av, t4)); c = __hadd2(c, __hgt2(av, t5)); c = __hadd2(c, __hgt2(av, t6));
-        uint32_t ci = *reinterpret_cast<const uint32_t*>(&c) & 0x00070007u;                  // two counts
-        const uint32_t nz = (ci + 0x00070007u) & 0x00080008u;                                // 8 where the count is not 0
-        ci |= (u[j] >> 12) & nz;                                                             // the sign bit, on non-zero codes only
-        const uint32_t byte = (ci | (ci >> 12)) & 0xffu;                                     // low nibble = even element
-        if (j < 4) lo |= byte << (8 * j); else hi |= byte << (8 * (j - 4));
+        const __nv_bfloat162 r0 = __hgt2(a[j], t0);
+        __nv_bfloat162 c = __hadd2(base, r0);
+        c = __hadd2(c, __hgt2(a[j], t1)); c = __hadd2(c, __hgt2(a[j], t2)); c = __hadd2(c, __hgt2(a[j], t3));
+        c = __hadd2(c, __hgt2(a[j], t4)); c = __hadd2(c, __hgt2(a[j], t5)); c = __hadd2(c, __hgt2(a[j], t6));
+        c = __hfma2(__hmul2(__hlt2(bf2(u[j]), zero), r0), eight, c);                // + 8 for a negative element with a non-zero count
+        n[j] = bits(c);                                                             // byte 0: code of element 2j, byte 2: of element 2j+1
     }
+    // low nibbles = even elements, high nibbles = odd elements
+    const uint32_t e_lo = __byte_perm(__byte_perm(n[0], n[1], 0x0040), __byte_perm(n[2], n[3], 0x0040), 0x5410);
+    const uint32_t o_lo = __byte_perm(__byte_perm(n[0], n[1], 0x0062), __byte_perm(n[2], n[3], 0x0062), 0x5410);
+    const uint32_t e_hi = __byte_perm(__byte_perm(n[4], n[5], 0x0040), __byte_perm(n[6], n[7], 0x0040), 0x5410);
+    const uint32_t o_hi = __byte_perm(__byte_perm(n[4], n[5], 0x0062), __byte_perm(n[6], n[7], 0x0062), 0x5410);
+    lo = e_lo | (o_lo << 4);
+    hi = e_hi | (o_hi << 4);
 }
 }  // namespace b200
