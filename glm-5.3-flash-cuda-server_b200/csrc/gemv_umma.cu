@@ -70,8 +70,11 @@ constexpr int UM_MAX_STAGES = 12;                  // TMEM holds one 16-column s
 constexpr int UM_MAX_STEPS = 64;                   // K <= 16384
 constexpr int UM_TMEM_COLS = 512;                  // D0..D3 [0,256), 64 each | unit scales [256,260) | weight scales from 272, 16 columns per slot
 constexpr int UM_COL_SB = 256, UM_COL_SF = 272;
-constexpr int UM_RES_ACC = 8, UM_RES_SB = 32, UM_RES_SF = 48;      // decode kernel with resident scales: D0..D3 [0,32) | unit scales [32,36) | step g's scales [48 + 16 g, ..)
-constexpr int UM_RES_STEPS = (UM_TMEM_COLS - UM_RES_SF) / 16;      // 29 steps: K <= 7424
+// Decode kernel with resident scales, up to UM_RES_MAX_M activation rows: accumulators D0..D3 at a stride of a columns
+// (8 for one row, 16 for two, 32 for three or four) | unit scales [4a, 4a + 4) | step g's scales [4a + 16 + 16 g, ..).
+constexpr int UM_RES_MAX_M = 4;
+static inline int um_res_acc_stride(int M) { return M <= 1 ? 8 : (M == 2 ? 16 : 32); }
+static inline int um_res_steps(int M) { return (UM_TMEM_COLS - (4 * um_res_acc_stride(M) + 16)) / 16; }      // 29 / 27 / 23 steps
 
 
 struct UmParams {
@@ -87,6 +90,8 @@ struct UmParams {
     uint32_t bimg_off, scl_off, tsc_off;           // shared-memory offsets of the B image, of the scale slabs and (resident scales) of their transposed copy from the (1 KB aligned) ring
     int ov_first;                                  // resident scales: stages from this one on share their bytes with the scale slabs or the transposed copy
     int early;                                     // stages requested by the producer before it waits for the other barriers (-1: not even the slabs)
+    int acc_stride;                                // resident scales: TMEM columns between the four accumulators
+    int require_res;                               // host only: refuse the launch unless it takes the resident-scales kernel
 };
 
 
@@ -129,13 +134,41 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
     // Pass A: amax of every activation row.  For M == 1 this thread's first 16-group stays in
     // registers for pass B (for K <= 4096 that is all of its work: one trip to memory, not two).
     float4 xv[4];
+    auto ab = [](float f) { return __float_as_uint(f) & 0x7fffffffu; };
+    if (!SINGLE && M >= 2 && M <= 4) {
+        // Two to four rows: the loads of all rows are issued before any row's maximum is reduced (one trip to
+        // memory for the pass instead of one per row).
+        uint32_t am[4] = {0u, 0u, 0u, 0u};
+        for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
+            #pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                if (m < M) {
+                    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
+                    const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
+                    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 v = ldx(xr, xr2, i + q);
+                        am[m] = max(am[m], max(max(ab(v.x), ab(v.y)), max(ab(v.z), ab(v.w))));
+                    }
+                }
+            }
+        }
+        #pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            if (m < M) {
+                uint32_t a = am[m];
+                #pragma unroll
+                for (int o = 16; o; o >>= 1) a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+                if (lane == 0) red[m][t4 >> 5] = __uint_as_float(a);
+            }
+        }
+    } else
     for (int m = 0; m < M; ++m) {
         const float4* xr = reinterpret_cast<const float4*>(x + (size_t)m * K);
         const float4* xr2 = x2 ? reinterpret_cast<const float4*>(x2 + (size_t)m * K) : nullptr;
         // The maximum is taken over the bit patterns of |x|: they order like the values, and an infinity or
         // a NaN (patterns from 0x7f800000 up) wins the maximum instead of being dropped as fmaxf would.
         uint32_t a = 0u;
-        auto ab = [](float f) { return __float_as_uint(f) & 0x7fffffffu; };
         for (int i = t4 * 4; i < (K >> 2); i += UM_WORKERS * 4) {
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -224,7 +257,7 @@ template <bool GEN, bool RES>
 __global__ void __launch_bounds__(UM_THREADS, 1)
 k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps maps) {
     static_assert(!(GEN && RES), "resident scales are a decode-kernel mode");
-    constexpr int COL_ACC = RES ? UM_RES_ACC : 64, COL_SB = RES ? UM_RES_SB : UM_COL_SB, COL_SF = RES ? UM_RES_SF : UM_COL_SF;
+    const int COL_ACC = RES ? p.acc_stride : 64, COL_SB = RES ? 4 * p.acc_stride : UM_COL_SB, COL_SF = RES ? 4 * p.acc_stride + 16 : UM_COL_SF;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t full_bar[UM_MAX_STEPS], sf_bar[UM_MAX_STEPS], empty_bar[UM_MAX_STEPS], done_bar, sc_bar, bi_bar, scd_bar;
     __shared__ uint32_t tmem_base_s;
@@ -250,7 +283,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
     }
     const int row0 = ((int)blockIdx.x - J.task0) * p.R * T;      // first row of the CTA's T tiles
     const int nsteps = T * nst;                      // step g: tile g / nst, 256-k block g % nst
-    const int M = GEN ? J.M : 1;
+    const int M = GEN ? J.M : (RES ? p.max_m : 1);   // the resident-scales kernel takes up to four rows (all jobs the same number)
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);      // SWIZZLE_128B tiles need 1 KB alignment
     unsigned char* bimg = ring + p.bimg_off;        // nst tiles of max_m KB: [step][row m][digit t][128 B]
     unsigned char* scl = ring + p.scl_off;          // all scale rows of the CTA: per tile, slabs [R x sc_box]
@@ -484,7 +517,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             if (t4 < M * UM_NB) (&gam[0][0])[t4] = J.gam[t4];
             UM_WAIT(smem_u32(&bi_bar), 0, p.status, 7);
         } else {
-            split_rows<!GEN>(J.x, GEN ? J.x2 : nullptr, p.limit, M, K, p.max_m, bimg, &gam[0][0], red, t4);
+            if (!GEN && M == 1) split_rows<true>(J.x, nullptr, p.limit, 1, K, p.max_m, bimg, &gam[0][0], red, t4);
+            else split_rows<false>(J.x, GEN ? J.x2 : nullptr, p.limit, M, K, p.max_m, bimg, &gam[0][0], red, t4);
         }
         fence_async_smem();
         tc_fence_before();
@@ -581,7 +615,7 @@ static bool make_map(CUtensorMap* m, const void* base, int rows, size_t row_byte
 
 // Conditions: M = 1 (one activation row shared by all jobs), K % 256 == 0 and K <= 16384, 16-byte
 // aligned tensors and activation, at least 256 rows in total.
-static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre);
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre, bool require_res = false);
 static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaStream_t s);
 
 // Rows of the activations are taken in chunks that fit the shared memory (the B image takes M KB
@@ -611,6 +645,12 @@ int nvfp4_multi_umma_ws(const GemvParams& g, int M, void* ws, cudaStream_t s) {
     if (M < 2 || !ws || ((uintptr_t)ws & 255) || (K & 255) || K > 16384) return B200_ENOTIMPL;
     for (int i = 0; i < g.n_jobs; ++i) if (g.j[i].x != g.j[0].x) return B200_ENOTIMPL;
     if ((uintptr_t)g.j[0].x & 15) return B200_ENOTIMPL;
+    // Up to four rows: one launch of the resident-scales kernel, which splits the rows itself (the same digits,
+    // so the same bits as the split-once path below), instead of a split launch and a product launch.
+    if (M <= UM_RES_MAX_M) {
+        const int rc = umma_launch(g, M, 0, s, nullptr, true);
+        if (rc != B200_ENOTIMPL) return rc;
+    }
     PreSplit pre{};
     pre.stride = std::min(M, UM_MAX_M);
     pre.chunk_bytes = (size_t)(K / 256) * pre.stride * 1024;
@@ -634,7 +674,7 @@ int nvfp4_multi_umma_ws(const GemvParams& g, int M, void* ws, cudaStream_t s) {
 }
 
 // One launch: activation rows [m0, m0 + M) of every job.
-static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre) {
+static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const PreSplit* pre, bool require_res) {
     const int K = g.K;
     if ((K & 255) || K > 16384 || !tmap_available()) return B200_ENOTIMPL;
     if (M < 1 || M > UM_MAX_M) return B200_ENOTIMPL;
@@ -651,6 +691,7 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
     UmParams p{};
     p.n_jobs = g.n_jobs; p.K = K; p.R = R; p.max_m = pre ? pre->stride : M; p.T = 1;
     p.dry_run = pre && pre->dry_run;
+    p.require_res = require_res ? 1 : 0;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     {
         // More tiles than SMs even at R = 128 (a vocabulary projection): several consecutive tiles per
@@ -688,8 +729,11 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
     // rows were loaded (the extra accumulator rows are never stored).  Keep that read inside the
     // allocation for the last stage as well.
     if (p.stage_bytes + fixed < 16384) fixed = 16384 - p.stage_bytes;
-    const bool gen = p.table != nullptr || p.max_m != 1 || p.T != 1;
-    const bool res = !gen && nst <= UM_RES_STEPS;
+    const bool presplit = p.table == nullptr && p.j[0].bimg != nullptr;
+    const bool res = p.table == nullptr && !presplit && p.T == 1 && p.max_m <= UM_RES_MAX_M && nst <= um_res_steps(p.max_m);
+    const bool gen = !res && (p.table != nullptr || p.max_m != 1 || p.T != 1);
+    if (p.require_res && !res) return B200_ENOTIMPL;
+    p.acc_stride = um_res_acc_stride(p.max_m);
     const int var = gen ? 0 : res ? 2 : 1;
     auto kern = gen ? k_gemv_umma<true, false> : res ? k_gemv_umma<false, true> : k_gemv_umma<false, false>;
     // static shared memory of the kernel and the device's opt-in limit: asked once per device and variant
@@ -714,7 +758,7 @@ static int umma_finish_launch(UmParams& p, const UmMaps& maps, int tasks, cudaSt
         // Ring | transposed scales | slabs | B image when everything fits; otherwise the transposed scales and
         // the slabs lie under the last stages of the ring (which wait until the scales are in TMEM), so that the
         // ring is as deep as the SM allows.
-        const size_t bimg = (size_t)nst * 1024, sc = ((size_t)R * (K / 16) + 1023) & ~(size_t)1023, tsc = (size_t)nsteps * 2048;
+        const size_t bimg = (size_t)nst * M * 1024, sc = ((size_t)R * (K / 16) + 1023) & ~(size_t)1023, tsc = (size_t)nsteps * 2048;
         if ((size_t)nsteps * p.stage_bytes + tsc + sc + bimg <= room) {
             p.stages = nsteps; p.tsc_off = (uint32_t)nsteps * p.stage_bytes; p.ov_first = nsteps;
             p.scl_off = p.tsc_off + (uint32_t)tsc;
