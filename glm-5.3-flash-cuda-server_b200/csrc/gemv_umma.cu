@@ -694,16 +694,30 @@ static int umma_launch(const GemvParams& g, int M, int m0, cudaStream_t s, const
     p.require_res = require_res ? 1 : 0;
     if (!scale_box(K, &p.sc_box, &p.sc_swz)) return B200_ENOTIMPL;
     {
-        // More tiles than SMs even at R = 128 (a vocabulary projection): several consecutive tiles per
-        // CTA, so that a CTA splits the activations and fills its pipeline once.  Same limits as the
-        // job-table launches; the results do not depend on T.
-        long tiles = 0;
-        for (int i = 0; i < g.n_jobs; ++i) tiles += (g.j[i].N + R - 1) / R;
-        const int nst = K / 256;
-        for (int T = 2; T * p.max_m <= 8; ++T) {
-            if (T * nst > UM_MAX_STEPS) break;
-            if ((size_t)T * R * (K / 16) + (size_t)nst * p.max_m * 1024 + 4 * (((size_t)R * 128 + 1023) & ~(size_t)1023) > 200 * 1024) break;
-            if (tiles / T >= nsm) p.T = T;
+        // More tiles than SMs even at R = 128 (a vocabulary projection, a fused pair of wide projections): a CTA
+        // takes T consecutive tiles of R rows, so that it splits the activations and fills its pipeline once.
+        // (R, T) by estimated time: a wave of CTAs costs its rows plus a fixed part worth about 40 rows; a last
+        // wave that fills only part of the SMs runs faster per CTA, but not below 0.4 of a full wave's time.
+        // Same limits as the job-table launches; the results do not depend on R or T.
+        long tiles128 = 0;
+        for (int i = 0; i < g.n_jobs; ++i) tiles128 += (g.j[i].N + 127) / 128;
+        // Up to two waves of single tiles stay as they are: one tile per CTA keeps the resident-scales kernel, whose
+        // fixed part is half the general kernel's, and the second wave starts SM by SM as the first one drains
+        // (two fused [12288 x 4096] projections: 192 single tiles 17 us, 96 CTAs of two tiles 22 us, measured).
+        if (tiles128 > 2 * nsm) {
+            const int nst = K / 256;
+            double best = -1.0;
+            for (int T = 1; T * p.max_m <= 8 && T * nst <= UM_MAX_STEPS; ++T)
+                for (int r = 32; r <= 128; r += 8) {
+                    if ((size_t)T * r * (K / 16) + (size_t)nst * p.max_m * 1024 + 4 * (((size_t)r * 128 + 1023) & ~(size_t)1023) > 200 * 1024) continue;
+                    long ctas = 0;
+                    for (int i = 0; i < g.n_jobs; ++i) ctas += ((g.j[i].N + r - 1) / r + T - 1) / T;
+                    const long full = ctas / nsm, rem = ctas - full * nsm;
+                    const double rows = (double)r * T;
+                    const double cost = full * (rows + 40.0) + (rem ? rows * std::max((double)rem / nsm, 0.4) + 40.0 : 0.0);
+                    if (best < 0.0 || cost < best - 1e-9 || (cost < best + 1e-9 && r > R)) { best = cost; R = r; p.T = T; }
+                }
+            p.R = R;
         }
     }
     int tasks = 0;

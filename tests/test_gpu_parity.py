@@ -203,6 +203,27 @@ def test_tensor_core_gemv_vs_oracle_and_row_invariance(N, K, M):
     assert P.device_status() == 0
 
 
+def test_many_wave_tiling_equals_single_tile_rows_bitwise():
+    """A projection with more than two waves of 128-row tiles is cut into CTAs of T tiles of R rows chosen by
+    estimated time; a row's result must not depend on that: rows [r0, r0 + n) of the big product equal the product
+    with those rows alone (one tile per CTA, another kernel variant) bit for bit, and both match the oracle."""
+    P, O = pkg(), oracle()
+    N, K, r0, n = 40000, 4096, 12345 - 12345 % 8, 2048
+    t = host_triple((N, K), 91)
+    W = dev_weight(t)
+    x = np.random.default_rng(92).normal(0, 1, (1, K)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((1, N), float('nan'), device='cuda')
+    P.gemm(W, xd, y)
+    sub = P.Nvfp4Weight(W.packed[r0:r0 + n], W.scale[r0:r0 + n], W.gscale)
+    ys = torch.full((1, n), float('nan'), device='cuda')
+    P.gemm(sub, xd, ys)
+    assert torch.equal(y[0, r0:r0 + n], ys[0])
+    ref = O.gemm(x, t[0][r0:r0 + n], t[1][r0:r0 + n], t[2])
+    close(ys.cpu().numpy(), ref)
+    assert P.device_status() == 0
+
+
 @pytest.mark.parametrize('N,K,M', [(1000, 4096, 2), (4096, 1024, 8), (700, 1536, 5), (300, 2048, 20), (129, 4096, 64), (300, 16384, 8), (129, 7168, 4)])
 def test_presplit_workspace_calls_equal_plain_calls_bitwise(N, K, M):
     """b200_nvfp4_gemm_ws / gemv_multi_ws split the activation rows once into caller scratch; the
