@@ -41,12 +41,20 @@
 // parked at the closing barrier is scheduled rarely: measured 20 % slower).  Before it exits a CTA
 // waits for the last tcgen05.commit arrival of every stage: an arrival still in flight would land
 // in the shared memory of the next CTA on that SM.
-// Decode kernel with RESIDENT scales (RES; one row, one tile, K <= 7424): TMEM has room for the scales of every
-// step at once, so the MMA warps (idle until the activations are split) move them all as soon as the slabs have
-// landed -- with weights declared stable that is before the dependency wait -- and the shared memory of the
-// slabs then serves as further ring stages.  For the
-// decode shapes (K = 4096, R <= 96) the ring then holds the CTA's whole tile: every weight byte is requested
-// before the wait, and after the activation split the MMAs run at issue speed.
+// Prologue without a CTA-wide barrier: warp 0 initialises the barriers of its own loads and requests the
+// slabs and the first four stages at once; the MMA warps initialise the other barriers, allocate TMEM and
+// arrive at named barrier 3, where only the producer waits; the workers go straight to the dependency
+// wait and the activation loads, and learn of everything else at named barrier 2.
+//
+// Decode kernel with RESIDENT scales (RES: up to four activation rows, one tile per CTA, K <= 7424 for one
+// row, 6912 for two, 5888 for three or four): TMEM has room for the scales of every step at once, so the MMA
+// warps (idle until the activations are split) move them all as soon as the slabs have landed -- with weights
+// declared stable that is before the dependency wait.  They transpose a step's 4 x 4 words in registers into
+// [k-block][32 rows][16 B] and the tensor core copies that to TMEM (tcgen05.cp 32x128b.warpx4, issued by the lane
+// that issues the step's MMAs, so the two are ordered without a wait).  The slabs and their transposed copy lie
+// under the last stages of the ring, which are requested once a tcgen05.commit says the copies are done.  For
+// the decode shapes (K = 4096, R <= 96, one row) the ring then holds the CTA's whole tile: every weight byte is
+// requested before the first MMA, and after the activation split the MMAs run at issue speed.
 // Every mbarrier wait is bounded (tma_pipe.cuh).  No cluster launch, no multicast.
 #include "b200_internal.h"
 #include "nvfp4_decode.cuh"
