@@ -181,7 +181,7 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float4 v = ldx(xr, xr2, i + q);
-                if (SINGLE && i == t4 * 4) xv[q] = v;
+                if ((SINGLE || M == 1) && i == t4 * 4) xv[q] = v;
                 a = max(a, max(max(ab(v.x), ab(v.y)), max(ab(v.z), ab(v.w))));
             }
         }
@@ -245,7 +245,7 @@ __device__ __forceinline__ void split_rows(const float* x, const float* x2, floa
     };
     if (SINGLE || M == 1) {
         const float inv = row_inv(0);
-        for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, SINGLE && g == t4);
+        for (int g = t4; g < (K >> 4); g += UM_WORKERS) split_group(0, g, inv, g == t4);
     } else {
         // two rows per trip: two independent dependency chains for the scheduler to interleave
         for (int m = 0; m < M; m += 2) {
@@ -469,8 +469,22 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             }
             __syncwarp();
         }
+        // General kernel: these warps are idle while the workers split the activations, so they move the scales of
+        // the steps of the ring's first round (a slot each, free at this point); the workers take over from there.
+        const int npre = RES ? 0 : (min(nsteps, p.stages) & ~1);       // even: the two worker groups keep their parity
+        if (!RES && npre > 0) {
+            UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
+            int t = 0, it = 0;
+            for (int g = 0; g < npre; ++g) {
+                uint4 v[4];
+                load_scales(t, it, v);
+                store_scales((uint32_t)g, v);
+                if (++it == nst) { it = 0; ++t; }
+            }
+        }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
+        for (int g = 0; g < npre; ++g) mbar_arrive(smem_u32(&sf_bar[g]));
         if (RES && warp - UM_LOAD_WARPS < nsteps)        // this warp's first step: its weights are awaited now rather than after the barrier
             UM_WAIT(full0 + (warp - UM_LOAD_WARPS) * 8, 0, p.status, 3);
         const int me = warp - UM_LOAD_WARPS;
@@ -491,6 +505,7 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 const uint64_t dA = dA0 + (((uint32_t)s * p.stage_bytes) >> 4), dB = dB0 + (uint32_t)(it * p.max_m) * 64u;
                 const uint32_t acc0 = it >= 4;                          // the first k-block of an accumulator starts it
                 UM_WAIT((RES ? full0 : sf0) + g * 8, 0, p.status, 3);      // resident scales: only the step's weights are awaited
+                if (!RES && g < npre) UM_WAIT(full0 + g * 8, 0, p.status, 2);   // scales moved ahead of the weights: wait for those too
                 tc_fence_after();
                 if (lane == 0) {
                     #pragma unroll
@@ -539,11 +554,12 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
             // go to the TMEM slot of its stage.
             const uint32_t full0 = smem_u32(&full_bar[0]), sf0 = smem_u32(&sf_bar[0]);
             const int grp = t4 >> 7;
-            int s = grp % p.stages;
+            const int g0 = (min(nsteps, p.stages) & ~1) + grp;        // the MMA warps moved the steps before that
+            int s = g0 % p.stages;
             UM_WAIT(smem_u32(&sc_bar), 0, p.status, 6);
             // Software-pipelined: the next step's scale bytes are read from shared memory while this
             // step's tcgen05.st is in flight.
-            int rt = grp / nst, rit = grp - rt * nst;                  // tile and k-block of the next step to read
+            int rt = g0 / nst, rit = g0 - rt * nst;                    // tile and k-block of the next step to read
             auto read_scales = [&](int g, uint4 (&v)[4]) {
                 // full[g] also says that the MMAs that last read this stage's scale slot are done
                 UM_WAIT(full0 + g * 8, 0, p.status, 2);
@@ -552,8 +568,8 @@ k_gemv_umma(const __grid_constant__ UmParams p, const __grid_constant__ UmMaps m
                 load_scales(t, it, v);
             };
             uint4 v[4], vn[4];
-            if (grp < nsteps) read_scales(grp, v);
-            for (int g = grp; g < nsteps; g += 2) {
+            if (g0 < nsteps) read_scales(g0, v);
+            for (int g = g0; g < nsteps; g += 2) {
                 store_scales((uint32_t)s, v);
                 if (g + 2 < nsteps) read_scales(g + 2, vn);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");

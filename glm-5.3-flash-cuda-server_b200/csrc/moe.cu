@@ -39,32 +39,43 @@ k_route(int32_t* __restrict__ sel, float* __restrict__ wts, const float* __restr
         const float* __restrict__ bias, int E, int K, float scaling, int norm_prob, const __grid_constant__ MoePlan plan) {
     const int tok = blockIdx.x, lane = threadIdx.x;
     logits += (size_t)tok * E; sel += (size_t)tok * K; wts += (size_t)tok * K;
-    float score[C], choice[C];
+    // Ranking values as unsigned keys that order like the floats (0 = not a candidate: padding, a NaN, anything
+    // at or below -1e30, or already taken), so that a round is two warp reductions -- the largest key, then the
+    // lowest expert index among the lanes that hold it -- instead of five rounds of three shuffles.
+    float score[C];
+    uint32_t key[C];
     #pragma unroll
     for (int j = 0; j < C; ++j) {
         const int i = lane + 32 * j;
+        score[j] = 0.f; key[j] = 0u;
         if (i < E) {
             score[j] = 1.f / (1.f + __expf(-logits[i]));
-            choice[j] = score[j] + bias[i];
-        } else { score[j] = 0.f; choice[j] = -3.0e38f; }
+            const float c = score[j] + bias[i];
+            const uint32_t u = __float_as_uint(c);
+            if (c > -1e30f) key[j] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        }
     }
+    uint32_t lk = 0u; int lj = 0; float ls = 0.f;   // this lane's best candidate: key, slot, gate value (lowest slot among equals)
+    auto local_best = [&]() {
+        lk = 0u; lj = 0; ls = 0.f;
+        #pragma unroll
+        for (int j = 0; j < C; ++j) if (key[j] > lk) { lk = key[j]; lj = j; ls = score[j]; }
+    };
+    local_best();
     float my_w = 0.f;                              // lane k keeps the k-th gate
     int my_e = 0;                                  // ... and the k-th expert
     for (int k = 0; k < K; ++k) {
-        float bv = -1e30f, bs = 0.f; int bi = 0x7fffffff;
-        #pragma unroll
-        for (int j = 0; j < C; ++j)
-            if (choice[j] > bv) { bv = choice[j]; bs = score[j]; bi = lane + 32 * j; }
-        #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bs = os; bi = oi; }
+        const uint32_t gmax = __reduce_max_sync(0xffffffffu, lk);
+        int bi = 0; float bs = 0.f;                // fewer than K candidates: expert 0 with gate 0, as the serial scan would leave it
+        if (gmax) {
+            bi = (int)__reduce_min_sync(0xffffffffu, lk == gmax ? (uint32_t)(lane + 32 * lj) : 0x7fffffffu);
+            bs = __shfl_sync(0xffffffffu, ls, bi & 31);
         }
-        if (bi >= E) bi = 0;                       // only if fewer than K finite candidates
-        #pragma unroll
-        for (int j = 0; j < C; ++j) if (lane + 32 * j == bi) choice[j] = -1e30f;
+        if (lane == (bi & 31)) {
+            #pragma unroll
+            for (int j = 0; j < C; ++j) if (j == (bi >> 5)) key[j] = 0u;
+            local_best();
+        }
         if (lane == k) { my_w = bs; my_e = bi; }
         if (lane == 0) sel[k] = bi;
     }
