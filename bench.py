@@ -201,8 +201,8 @@ def bench_siblings(P, M, steps, warmup, copies, sampler_index=None):
 
 
 def bench_siblings_e2e(P, state, steps, warmup):
-    """Host buffers: x from pinned memory in, the six outputs (one device buffer) back to pinned memory, a
-    stream synchronisation per step.  The loop itself is C++ against the C ABI (tests/cpp/e2e_loop.cu), the way
+    """Host buffers: x from pinned memory in, the six outputs (one device buffer) back to pinned memory (copy,
+    product and copy replayed as one graph launch per step), a stream synchronisation per step.  The loop itself is C++ against the C ABI (tests/cpp/e2e_loop.cu), the way
     an engine like the reference's calls this path; Python only hands over the pointers."""
     import ctypes as C
     sets, x, ys, jobs, ybuf = state
@@ -219,10 +219,12 @@ def bench_siblings_e2e(P, state, steps, warmup):
         for i in range(n):
             rot[c * n + i] = j[i]
     rc = C.c_int(0)
-    s = torch.cuda.current_stream()
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()                      # a stream of its own: the loop captures its step into graphs, which the legacy default stream cannot do
     ms = L.e2e_gemv_multi_loop(rot, len(jobs), n, M, K_HID, C.c_void_p(xh.data_ptr()), C.c_void_p(x.data_ptr()), C.c_size_t(M * K_HID * 4),
                                C.c_void_p(ybuf.data_ptr()), C.c_void_p(yh.data_ptr()), C.c_size_t(ybuf.numel() * 4),
                                int(steps), int(warmup), C.c_void_p(s.cuda_stream), C.byref(rc))
+    torch.cuda.synchronize()
     if rc.value:
         raise SystemExit('end-to-end loop failed: status %d' % rc.value)
     return ms, M * K_HID * 4, M * sum(SIBLINGS) * 4
