@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Generates tests/golden/*.npz by running the REFERENCE's own Python code on seeded inputs.
 
-Run once in a container that has the reference checkout (default /root/reference, or pass its
-path); the outputs are committed and are what pins the CPU oracle.  Nothing at test time reads
+Run once in a container that has the reference checkout (pass its path, or rely on the default
+below); the outputs are committed and are what pins the CPU oracle.  Nothing at test time reads
 the reference checkout.
 
     python tests/golden/make_golden.py [/path/to/reference]
